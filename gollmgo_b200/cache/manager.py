@@ -38,6 +38,8 @@ class PagedKVNeed:
     shared_kv: bool = False           # keys and values are one tensor (a latent both are expanded from)
     v_heads: Optional[int] = None     # value heads and their size where they differ from the keys'
     v_head_dim: Optional[int] = None  # (None: as the keys); values then live in a tensor of their own
+    keep_first: int = 0               # with a window: the first tokens of a sequence stay visible behind it,
+                                      # so the pages that hold them are never given back
 
     @property
     def split_kv(self) -> bool:
@@ -210,11 +212,12 @@ class CacheManager:
         if w is None:
             return []
         first_needed = rc.num_tokens - w + 1          # oldest key the next token may read
+        kept = -(-self.groups[gi].need.keep_first // self.page_size)     # pages with tokens that stay visible
         out = []
         for idx, page in enumerate(rc.pages[gi]):
             if (idx + 1) * self.page_size > first_needed:
                 break
-            if page >= 0:
+            if page >= 0 and idx >= kept:
                 out.append(idx)
         return out
 
@@ -262,7 +265,7 @@ class CacheManager:
         limit = None
         for g in self.groups:
             pool = g.pool.num_pages * self.page_size
-            if g.need.window is not None and pool >= g.need.window + portion + 2 * self.page_size:
+            if g.need.window is not None and pool >= g.need.window + g.need.keep_first + portion + 3 * self.page_size:
                 continue
             limit = pool if limit is None else min(limit, pool)
         return limit

@@ -24,8 +24,8 @@
 
 template <typename TA, int DMAX>
 __device__ __forceinline__ void attn_tile(const AttnArgs& a, int nrows, const TA* const* qptr_s,
-                                          const int* pos_s, int kvh, const int* bt, int lo,
-                                          int hi, float* smem, float* acc) {
+                                          const int* pos_s, const int* head_s, int kvh, const int* bt, int lo_main,
+                                          int hi_main, int first_hi, float* smem, float* acc) {
   constexpr int NACC = ATT_BQ * DMAX / ATT_THREADS;
   const int d = a.d, dv = a.dv > 0 ? a.dv : a.d, ps = a.page_size;
   const int vsh = a.v_share > 1 ? a.v_share : 1, nv = a.nkv / vsh, vh = kvh / vsh;
@@ -49,6 +49,10 @@ __device__ __forceinline__ void attn_tile(const AttnArgs& a, int nrows, const TA
   for (int i = 0; i < NACC; ++i) acc[i] = 0.f;
   __syncthreads();
 
+  // two runs of keys: the first tokens that stay visible behind the window, [0, first_hi), where
+  // there are any (first_hi <= lo), then [lo, hi)
+  for (int run = first_hi > 0 ? 0 : 1; run < 2; ++run) {
+  const int lo = run ? lo_main : 0, hi = run ? hi_main : first_hi;
   const int kstart = (lo / ATT_BK) * ATT_BK;
   for (int kb = kstart; kb < hi; kb += ATT_BK) {
     // ---- stage keys and values of tokens [kb, kb+64)
@@ -84,9 +88,11 @@ __device__ __forceinline__ void attn_tile(const AttnArgs& a, int nrows, const TA
       for (int i = 0; i < 8; ++i) {
         const int r = rb + 2 * i;
         const int p = pos_s[r];
-        const bool ok = tok >= lo && tok < hi && tok <= p && (a.window <= 0 || tok > p - a.window);
+        const bool ok = tok >= lo && tok < hi && tok <= p && (a.window <= 0 || tok > p - a.window || tok < a.keep_first);
         float sc = s[i] * a.scale;
         if (a.softcap > 0.f) sc = a.softcap * tanhf(sc / a.softcap);
+        if (ok && a.dist_bias) sc += a.dist_bias[(size_t)a.dist_bucket[min(p - tok, a.dist_max)] * a.nh + head_s[r]];
+        if (ok && a.head_bias) sc += a.head_bias[head_s[r]];
         Ss[r * ATT_BK + j] = ok ? sc : -INFINITY;
       }
     }
@@ -96,6 +102,12 @@ __device__ __forceinline__ void attn_tile(const AttnArgs& a, int nrows, const TA
     for (int i = 0; i < 4; ++i) {
       const int r = warp * 4 + i;
       const float s0 = Ss[r * ATT_BK + lane], s1 = Ss[r * ATT_BK + lane + 32];
+      if (a.weights == 1) {                        // a weight per key on its own: no maximum, no sum, nothing to rescale
+        Ss[r * ATT_BK + lane] = 1.f / (1.f + expf(-s0));
+        Ss[r * ATT_BK + lane + 32] = 1.f / (1.f + expf(-s1));
+        if (lane == 0) { m_s[r] = 0.f; l_s[r] = 1.f; }
+        continue;
+      }
       const float mx = warp_max(fmaxf(s0, s1));
       const float m_old = m_s[r];
       const float m_new = fmaxf(m_old, mx);
@@ -127,6 +139,7 @@ __device__ __forceinline__ void attn_tile(const AttnArgs& a, int nrows, const TA
     }
     __syncthreads();
   }
+  }
 }
 
 __host__ __device__ constexpr int attn_smem_floats(int d, int dv) {
@@ -145,6 +158,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_prefill_kernel(AttnArgs a) {
   extern __shared__ float smem[];
   __shared__ const TA* qptr_s[ATT_BQ];
   __shared__ int pos_s[ATT_BQ];
+  __shared__ int head_s[ATT_BQ];
   pdl_wait();
   const int b = a.tile_seq[blockIdx.x], q0 = a.tile_q0[blockIdx.x];
   const int h = blockIdx.y, kvh = h / (a.nh / a.nkv);
@@ -156,12 +170,14 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_prefill_kernel(AttnArgs a) {
     const int r = threadIdx.x;
     qptr_s[r] = r < nrows ? (const TA*)a.q + (size_t)(t0 + q0 + r) * a.q_stride + (size_t)h * a.d : nullptr;
     pos_s[r] = r < nrows ? qstart + q0 + r : -1;
+    head_s[r] = h;
   }
   __syncthreads();
   const int first = qstart + q0, last = first + nrows - 1;
   const int lo = a.window > 0 ? max(0, first - a.window + 1) : 0;
   float acc[NACC];
-  attn_tile<TA, DMAX>(a, nrows, qptr_s, pos_s, kvh, a.block_tables + (size_t)b * a.bt_stride, lo, last + 1, smem, acc);
+  attn_tile<TA, DMAX>(a, nrows, qptr_s, pos_s, head_s, kvh, a.block_tables + (size_t)b * a.bt_stride, lo, last + 1,
+                      min(a.keep_first, lo), smem, acc);
   pdl_trigger();
   const float* l_s = attn_tile_max(a, smem) + ATT_BQ;
   const int dv = a.dv > 0 ? a.dv : a.d;
@@ -189,6 +205,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(AttnArgs a) {
   extern __shared__ float smem[];
   __shared__ const TA* qptr_s[ATT_BQ];
   __shared__ int pos_s[ATT_BQ];
+  __shared__ int head_s[ATT_BQ];
   pdl_wait();
   const int G = a.nh / a.nkv, gchunks = (G + ATT_BQ - 1) / ATT_BQ;
   const int b = a.dec_seqs[blockIdx.x];
@@ -206,11 +223,14 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(AttnArgs a) {
     const int r = threadIdx.x;
     qptr_s[r] = r < nrows ? (const TA*)a.q + (size_t)t * a.q_stride + (size_t)(kvh * G + g0 + r) * a.d : nullptr;
     pos_s[r] = r < nrows ? ctx - 1 : -1;
+    head_s[r] = kvh * G + g0 + (r < nrows ? r : 0);
   }
   __syncthreads();
   float acc[NACC];
   if (lo < hi) {
-    attn_tile<TA, DMAX>(a, nrows, qptr_s, pos_s, kvh, a.block_tables + (size_t)b * a.bt_stride, lo, hi, smem, acc);
+    // the first slice also takes the first tokens that stay visible behind the window
+    attn_tile<TA, DMAX>(a, nrows, qptr_s, pos_s, head_s, kvh, a.block_tables + (size_t)b * a.bt_stride, lo, hi,
+                        split == 0 ? min(a.keep_first, lo0) : 0, smem, acc);
   } else {
 #pragma unroll
     for (int i = 0; i < NACC; ++i) acc[i] = 0.f;
@@ -255,6 +275,16 @@ __global__ void attn_merge_kernel(AttnArgs a) {
     if (m != -INFINITY) L += expf(m - M) * a.part_ml[(row0 + s) * 2 + 1];
   }
   const size_t at = (size_t)t * a.nh * d + (size_t)h * d;
+  if (a.weights == 1) {                            // weights that are not normalised: the slices' sums add up
+    for (int c = threadIdx.x; c < d; c += blockDim.x) {
+      float o = 0.f;
+      for (int s = 0; s < S; ++s)
+        if (a.part_ml[(row0 + s) * 2] != -INFINITY) o += a.part_o[(row0 + s) * d + c];
+      if (a.out_f32) ((float*)a.out)[at + c] = o;
+      else ((TA*)a.out)[at + c] = from_f32<TA>(o);
+    }
+    return;
+  }
   for (int c = threadIdx.x; c < d; c += blockDim.x) {
     float o = 0.f;
     for (int s = 0; s < S; ++s) {
@@ -486,7 +516,9 @@ extern "C" int gg_attn_prefill_x(const void* q, long long q_stride, const void* 
                                  const int* context_lens, const int* tile_seq, const int* tile_q0, int num_tiles,
                                  const int* tile64_seq, const int* tile64_q0, int num_tiles64, int allow_mma,
                                  void* out, int out_f32, int nh, int nkv, int d, int dv, int v_share,
-                                 int page_size, int window, float scale, float softcap, cudaStream_t stream) {
+                                 int page_size, int window, float scale, float softcap, int keep_first, int weights,
+                                 const float* head_bias, const float* dist_bias, const int* dist_bucket, int dist_max,
+                                 cudaStream_t stream) {
   AttnArgs a = {};
   a.q = q; a.q_stride = q_stride; a.kcache = kcache; a.vcache = vcache;
   a.block_tables = block_tables; a.bt_stride = bt_stride; a.cu_q_lens = cu_q_lens;
@@ -494,10 +526,15 @@ extern "C" int gg_attn_prefill_x(const void* q, long long q_stride, const void* 
   a.page_size = page_size; a.window = window; a.scale = scale;
   a.dv = dv; a.v_share = v_share; a.softcap = softcap; a.out_f32 = out_f32;
   a.tile_seq = tile_seq; a.tile_q0 = tile_q0;
+  a.keep_first = window > 0 ? keep_first : 0; a.weights = weights; a.head_bias = head_bias;
+  a.dist_bias = dist_bias; a.dist_bucket = dist_bucket; a.dist_max = dist_max;
   int rc = check_common(a, "attn_prefill_x");
   if (rc) return rc;
+  GG_REQUIRE(weights == 0 || weights == 1, "attn_prefill_x: unknown kind of weights %d", weights);
+  GG_REQUIRE(!dist_bias || (dist_bucket && dist_max >= 0), "attn_prefill_x: a distance bias needs its bucket table");
+  const bool plain = !a.keep_first && !weights && !head_bias && !dist_bias;   // what the mma.sync kernels compute
   // bfloat16 with sizes of 64 or 128: the mma.sync kernel over tiles of 64 queries
-  if (allow_mma && tile64_seq && attn_mma_x_supported(dtype, d, dv > 0 ? dv : d, page_size) && q_stride % 8 == 0) {
+  if (plain && allow_mma && tile64_seq && attn_mma_x_supported(dtype, d, dv > 0 ? dv : d, page_size) && q_stride % 8 == 0) {
     a.tile_seq = tile64_seq; a.tile_q0 = tile64_q0;
     return attn_prefill_mma_x(a, num_tiles64, stream);
   }
@@ -509,7 +546,8 @@ extern "C" int gg_attn_decode_x(const void* q, long long q_stride, const void* k
                                 const int* context_lens, const int* dec_seqs, int n_dec, int num_splits,
                                 float* part_o, float* part_ml, void* out, int out_f32, int nh, int nkv, int d,
                                 int dv, int v_share, int page_size, int window, float scale, float softcap,
-                                int allow_mma, cudaStream_t stream) {
+                                int allow_mma, int keep_first, int weights, const float* head_bias,
+                                const float* dist_bias, const int* dist_bucket, int dist_max, cudaStream_t stream) {
   AttnArgs a = {};
   a.q = q; a.q_stride = q_stride; a.kcache = kcache; a.vcache = vcache;
   a.block_tables = block_tables; a.bt_stride = bt_stride; a.cu_q_lens = cu_q_lens;
@@ -517,8 +555,13 @@ extern "C" int gg_attn_decode_x(const void* q, long long q_stride, const void* k
   a.page_size = page_size; a.window = window; a.scale = scale;
   a.dv = dv; a.v_share = v_share; a.softcap = softcap; a.out_f32 = out_f32;
   a.dec_seqs = dec_seqs; a.num_splits = num_splits; a.part_o = part_o; a.part_ml = part_ml;
+  a.keep_first = window > 0 ? keep_first : 0; a.weights = weights; a.head_bias = head_bias;
+  a.dist_bias = dist_bias; a.dist_bucket = dist_bucket; a.dist_max = dist_max;
   int rc = check_common(a, "attn_decode_x");
   if (rc) return rc;
+  GG_REQUIRE(weights == 0 || weights == 1, "attn_decode_x: unknown kind of weights %d", weights);
+  GG_REQUIRE(!dist_bias || (dist_bucket && dist_max >= 0), "attn_decode_x: a distance bias needs its bucket table");
+  if (a.keep_first || weights || head_bias || dist_bias) allow_mma = 0;       // the general kernel has these
   GG_REQUIRE(n_dec >= 0 && num_splits >= 1 && num_splits <= 65535, "attn_decode_x: bad n_dec %d or splits %d", n_dec, num_splits);
   GG_REQUIRE(part_o && part_ml, "attn_decode_x: no scratch given");
   if (n_dec == 0) return GG_OK;

@@ -34,6 +34,12 @@ struct AttnArgs {
   int v_share;              // this many consecutive key heads read one value head (0 or 1: each its own)
   float softcap;            // > 0: score <- softcap * tanh(score / softcap) after the scaling
   int out_f32;              // out is float32 [T, nh*dv] whatever the cache's type
+  int keep_first;           // with a window: keys at positions < keep_first stay visible behind it
+  int weights;              // 0: softmax over the visible keys; 1: every visible key weighs sigmoid(score + head_bias[h]), not normalised
+  const float* head_bias;   // [nh] (weights == 1), or null
+  const float* dist_bias;   // [rows, nh]: row dist_bucket[min(i - j, dist_max)] is added to the scaled score; null = none
+  const int* dist_bucket;   // [dist_max + 1]
+  int dist_max;
 };
 
 // General kernels (attention.cu)

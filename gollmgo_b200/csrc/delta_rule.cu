@@ -8,7 +8,8 @@
 // Three kernels a step, every one for any mix of prompt portions and single decoded tokens:
 //   delta_prep     per (token, head unit): convolution + SiLU, unit norms, beta and decay
 //   delta_recur    per (sequence, head, 16 value columns): the recurrence over the portion
-//   delta_out      per (token, head): o / rms(o) * weight * silu(gate)
+//   delta_out      per (token, head): o / rms(o) * weight * silu(gate)  (or sigmoid(gate))
+// The decay is one number per head and token, or one per head, token and key channel (a row of S).
 // and delta_conv_state, which moves the convolution's window on after delta_prep has read it.
 // Every column j of S evolves on its own (S[:, j] only ever meets v_j and u_j), so the columns
 // of a head are spread over CTAs; eight lanes share a column and split its d rows.
@@ -35,7 +36,8 @@ __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log
 // [slots, taps-1, C] holds the inputs at positions start-(taps-1) .. start-1 of the sequence.
 template <typename TA>
 __global__ void delta_prep_kernel(const TA* __restrict__ x, long long x_stride, const float* __restrict__ conv_w,
-                                  const float* __restrict__ conv_state, const float* __restrict__ ba,
+                                  const float* __restrict__ conv_state, const float* __restrict__ zb_in, long long zb_stride,
+                                  const float* __restrict__ za_in, long long za_stride, int dw,
                                   const float* __restrict__ a_log, const float* __restrict__ dt_bias,
                                   const int* __restrict__ cu_q_lens, const int* __restrict__ context_lens,
                                   const int* __restrict__ state_slots, int B, int G, int H, int d, int dv, int taps,
@@ -50,11 +52,11 @@ __global__ void delta_prep_kernel(const TA* __restrict__ x, long long x_stride, 
   const int start = context_lens[b] - qlen;            // tokens of the sequence before this step
   pdl_wait();
   if (u == 2 * G + H) {
-    for (int h = threadIdx.x; h < H; h += blockDim.x) {
-      const float zb = ba[(size_t)t * 2 * H + h], za = ba[(size_t)t * 2 * H + H + h];
-      beta[(size_t)t * H + h] = 1.f / (1.f + expf(-zb));
-      decay[(size_t)t * H + h] = expf(-expf(a_log[h]) * softplus_f(za + dt_bias[h]));
-    }
+    // dw = 1: one decay per head; dw = d: one per head and key channel
+    for (int h = threadIdx.x; h < H; h += blockDim.x)
+      beta[(size_t)t * H + h] = 1.f / (1.f + expf(-zb_in[(size_t)t * zb_stride + h]));
+    for (int e = threadIdx.x; e < H * dw; e += blockDim.x)
+      decay[(size_t)t * H * dw + e] = expf(-expf(a_log[e / dw]) * softplus_f(za_in[(size_t)t * za_stride + e] + dt_bias[e]));
     return;
   }
   const bool unit = u < 2 * G;                           // a q or k head: made a unit vector
@@ -118,6 +120,8 @@ __global__ void delta_conv_state_kernel(const TA* __restrict__ x, long long x_st
 #define DR_LANES 8          // lanes that share a column: lane r holds rows r, r + 8, r + 16, ... of it
 #define DR_CHUNK 16         // tokens staged in shared memory at a time
 #define DR_STAGE_FLOATS(dp) (2 * DR_CHUNK * (dp) + DR_CHUNK * DR_COLS + 2 * DR_CHUNK)
+// with a decay per key channel a stage also holds the decays [CHUNK][dp]
+#define DR_STAGE_FLOATS_X(dp, ch) (DR_STAGE_FLOATS(dp) + ((ch) ? DR_CHUNK * (dp) : 0))
 
 __device__ __forceinline__ void dr_cp16(float* dst, const float* src, int bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src), "r"(bytes) : "memory");
@@ -126,8 +130,11 @@ __device__ __forceinline__ void dr_cp4(float* dst, const float* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
 }
 
-// grid (B, H, ceil(dv / 16)), 128 threads.  state [slots, H, dv, d].
-template <int DPT>
+// grid (B, H, ceil(dv / 16)), 128 threads.  state [slots, H, dv, d].  CH: decay is [T, H, d], one
+// factor per row of S (key channel), and acts before the token's read and write: S <- diag(g) S.
+// DELTA = false: the plain linear recurrence S <- g S + k (beta v)^T; o = S^T q (a state-space layer:
+// k = B, q = C, v = x, beta = the step size): the token's write does not look at what S holds.
+template <int DPT, bool CH, bool DELTA>
 __global__ void __launch_bounds__(DR_COLS * DR_LANES)
 delta_recur_kernel(const float* __restrict__ qkv, const float* __restrict__ beta, const float* __restrict__ decay,
                    float* __restrict__ state, const int* __restrict__ cu_q_lens, const int* __restrict__ context_lens,
@@ -144,7 +151,7 @@ delta_recur_kernel(const float* __restrict__ qkv, const float* __restrict__ beta
   const int kvh = h / (H / G);
   const int dp = DPT * DR_LANES;                 // d rounded up to what the lanes hold
   float* ks = sm;                                // two stages of k [CHUNK][dp], q [CHUNK][dp], v [CHUNK][COLS], (beta, decay) [CHUNK][2]
-  float* os = sm + 2 * DR_STAGE_FLOATS(dp);      // [CHUNK][COLS]
+  float* os = sm + 2 * DR_STAGE_FLOATS_X(dp, CH);      // [CHUNK][COLS]
   const bool live = col < dv;
   float S[DPT];
   float* srow = state + (((size_t)slot * H + h) * dv + (live ? col : 0)) * d;
@@ -160,10 +167,26 @@ delta_recur_kernel(const float* __restrict__ qkv, const float* __restrict__ beta
   const bool vec = (d & 3) == 0 && (dv & 3) == 0;
   auto stage = [&](int c0, int buf) {
     const int n = min(DR_CHUNK, qlen - c0);
-    float* kb = ks + buf * DR_STAGE_FLOATS(dp);
+    float* kb = ks + buf * DR_STAGE_FLOATS_X(dp, CH);
     float* qb = kb + DR_CHUNK * dp;
     float* vb = qb + DR_CHUNK * dp;
     float* gb = vb + DR_CHUNK * DR_COLS;
+    float* cb = gb + 2 * DR_CHUNK;                 // CH: the decays of the chunk's tokens
+    if (CH) {
+      if (vec) {
+        const int per = dp >> 2;
+        for (int e = tid; e < n * per; e += blockDim.x) {
+          const int tt = e / per, row = (e - tt * per) << 2;
+          const int bytes = row < d ? 16 : 0;
+          dr_cp16(cb + tt * dp + row, decay + ((size_t)(t0 + c0 + tt) * H + h) * d + (bytes ? row : 0), bytes);
+        }
+      } else {
+        for (int e = tid; e < n * dp; e += blockDim.x) {
+          const int tt = e / dp, row = e - tt * dp;
+          cb[e] = row < d ? decay[((size_t)(t0 + c0 + tt) * H + h) * d + row] : 0.f;
+        }
+      }
+    }
     if (vec) {
       const int per = dp >> 2;
       for (int e = tid; e < n * per; e += blockDim.x) {
@@ -192,7 +215,7 @@ delta_recur_kernel(const float* __restrict__ qkv, const float* __restrict__ beta
     }
     if (tid < n) {
       dr_cp4(gb + tid * 2, beta + (size_t)(t0 + c0 + tid) * H + h);
-      dr_cp4(gb + tid * 2 + 1, decay + (size_t)(t0 + c0 + tid) * H + h);
+      if (!CH) dr_cp4(gb + tid * 2 + 1, decay + (size_t)(t0 + c0 + tid) * H + h);
     }
   };
   stage(0, 0);
@@ -203,28 +226,33 @@ delta_recur_kernel(const float* __restrict__ qkv, const float* __restrict__ beta
     asm volatile("cp.async.commit_group;" ::: "memory");
     asm volatile("cp.async.wait_group 1;" ::: "memory");
     __syncthreads();
-    const float* kc = ks + buf * DR_STAGE_FLOATS(dp);
+    const float* kc = ks + buf * DR_STAGE_FLOATS_X(dp, CH);
     const float* qc = kc + DR_CHUNK * dp;
     const float* vcur = qc + DR_CHUNK * dp;
     const float* bg = vcur + DR_CHUNK * DR_COLS;
+    const float* gc = bg + 2 * DR_CHUNK;
 #pragma unroll 2
     for (int tt = 0; tt < n; ++tt) {
       // lane r reads rows r, r + 8, ...: neighbouring lanes read neighbouring words (no bank
       // conflicts), and the sums run in four chains so that the additions overlap
       const float* kr = kc + tt * dp + r;
       const float* qr = qc + tt * dp + r;
-      const float be = bg[tt * 2], g = bg[tt * 2 + 1];
+      const float be = bg[tt * 2], g = CH ? 1.f : bg[tt * 2 + 1];
       float kv[DPT];
       float d4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int i = 0; i < DPT; ++i) {
         kv[i] = kr[i * DR_LANES];
-        d4[i & 3] = fmaf(kv[i], S[i], d4[i & 3]);
+        if (CH) S[i] *= gc[tt * dp + r + i * DR_LANES];          // every row by its own factor, first
+        if (DELTA) d4[i & 3] = fmaf(kv[i], S[i], d4[i & 3]);
       }
-      float dot = (d4[0] + d4[1]) + (d4[2] + d4[3]);
-      dot += __shfl_xor_sync(0xffffffffu, dot, 1);
-      dot += __shfl_xor_sync(0xffffffffu, dot, 2);
-      dot += __shfl_xor_sync(0xffffffffu, dot, 4);
+      float dot = 0.f;
+      if (DELTA) {
+        dot = (d4[0] + d4[1]) + (d4[2] + d4[3]);
+        dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+        dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+        dot += __shfl_xor_sync(0xffffffffu, dot, 4);
+      }
       const float u = be * (vcur[tt * DR_COLS + cl] - g * dot);
       float o4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -258,7 +286,7 @@ delta_recur_kernel(const float* __restrict__ qkv, const float* __restrict__ beta
 // grid (T, H): out[t, h, :] = o / sqrt(mean(o^2) + eps) * w * silu(gate[t, h, :])
 template <typename TA>
 __global__ void delta_out_kernel(const float* __restrict__ o_raw, const TA* __restrict__ gate, long long gate_stride,
-                                 const float* __restrict__ w, float eps, int H, int dv, TA* __restrict__ out) {
+                                 const float* __restrict__ w, float eps, int H, int dv, int gate_act, TA* __restrict__ out) {
   __shared__ float red[33];
   pdl_trigger();
   pdl_wait();
@@ -269,16 +297,34 @@ __global__ void delta_out_kernel(const float* __restrict__ o_raw, const TA* __re
   const float f = rsqrtf(block_sum(ss, red) / (float)dv + eps);
   const TA* gr = gate + (size_t)t * gate_stride + (size_t)h * dv;
   TA* y = out + (size_t)t * H * dv + (size_t)h * dv;
-  for (int c = threadIdx.x; c < dv; c += blockDim.x) y[c] = from_f32<TA>(o[c] * f * w[c] * silu_f(to_f32(gr[c])));
+  for (int c = threadIdx.x; c < dv; c += blockDim.x) {
+    const float z = to_f32(gr[c]);
+    y[c] = from_f32<TA>(o[c] * f * w[c] * (gate_act == 1 ? 1.f / (1.f + expf(-z)) : silu_f(z)));
+  }
 }
 
 // ---------------------------------------------------------------- launchers
+// The window of a short convolution over the C channels x[:, 0 .. C) moved on by this step's tokens
+// (also for the state-space layer, ssm.cu).
+int conv_state_update(const void* x, long long x_stride, int dtype, float* conv_state, const int* cu_q_lens,
+                      const int* context_lens, const int* state_slots, int B, int C, int taps, cudaStream_t stream) {
+  const dim3 sgrid(B, (C + 127) / 128);
+  if (dtype == GG_F32)
+    gg_launch(delta_conv_state_kernel<float>, sgrid, dim3(128), 0, stream, (const float*)x, x_stride, conv_state, cu_q_lens, context_lens, state_slots, C, taps);
+  else
+    gg_launch(delta_conv_state_kernel<__nv_bfloat16>, sgrid, dim3(128), 0, stream, (const __nv_bfloat16*)x, x_stride, conv_state, cu_q_lens, context_lens, state_slots, C, taps);
+  return gg_check_launch("conv_state_update");
+}
+
 extern "C" int gg_delta_prep(const void* x, long long x_stride, int dtype, const float* conv_w, float* conv_state,
-                             const float* ba, const float* a_log, const float* dt_bias, const int* cu_q_lens,
+                             const float* zb, long long zb_stride, const float* za, long long za_stride, int dw,
+                             const float* a_log, const float* dt_bias, const int* cu_q_lens,
                              const int* context_lens, const int* state_slots, int T, int B, int G, int H, int d, int dv,
                              int taps, float* qkv_out, float* beta, float* decay, cudaStream_t stream) {
   GG_REQUIRE(T >= 0 && B > 0 && G > 0 && H > 0 && H % G == 0 && d > 0 && dv > 0, "delta_prep: bad sizes T=%d B=%d G=%d H=%d d=%d dv=%d", T, B, G, H, d, dv);
   GG_REQUIRE(taps >= 1 && taps <= 17, "delta_prep: %d taps are outside 1..17", taps);
+  GG_REQUIRE(dw == 1 || dw == d, "delta_prep: a decay per head (1) or per key channel (%d), not %d", d, dw);
+  GG_REQUIRE(zb && za && zb_stride >= H && za_stride >= (long long)H * dw, "delta_prep: the inputs of beta and of the decay are missing or too short");
   const int C = 2 * G * d + H * dv;
   GG_REQUIRE(x_stride >= C, "delta_prep: rows of %lld values hold no %d channels", x_stride, C);
   if (T == 0) return GG_OK;
@@ -289,44 +335,46 @@ extern "C" int gg_delta_prep(const void* x, long long x_stride, int dtype, const
   const dim3 grid(T, 2 * G + H + 1);
   GG_REQUIRE(grid.y <= 65535, "delta_prep: too many heads");
   if (dtype == GG_F32)
-    gg_launch(delta_prep_kernel<float>, grid, dim3(threads), smem, stream, (const float*)x, x_stride, conv_w, (const float*)conv_state, ba, a_log, dt_bias, cu_q_lens, context_lens, state_slots, B, G, H, d, dv, taps, qkv_out, beta, decay);
+    gg_launch(delta_prep_kernel<float>, grid, dim3(threads), smem, stream, (const float*)x, x_stride, conv_w, (const float*)conv_state, zb, zb_stride, za, za_stride, dw, a_log, dt_bias, cu_q_lens, context_lens, state_slots, B, G, H, d, dv, taps, qkv_out, beta, decay);
   else if (dtype == GG_BF16)
-    gg_launch(delta_prep_kernel<__nv_bfloat16>, grid, dim3(threads), smem, stream, (const __nv_bfloat16*)x, x_stride, conv_w, (const float*)conv_state, ba, a_log, dt_bias, cu_q_lens, context_lens, state_slots, B, G, H, d, dv, taps, qkv_out, beta, decay);
+    gg_launch(delta_prep_kernel<__nv_bfloat16>, grid, dim3(threads), smem, stream, (const __nv_bfloat16*)x, x_stride, conv_w, (const float*)conv_state, zb, zb_stride, za, za_stride, dw, a_log, dt_bias, cu_q_lens, context_lens, state_slots, B, G, H, d, dv, taps, qkv_out, beta, decay);
   else
     return gg_fail(GG_ERR_INVALID, "delta_prep: unknown dtype %d", dtype);
   int rc = gg_check_launch("delta_prep");
   if (rc || taps == 1) return rc;
-  const dim3 sgrid(B, (C + 127) / 128);
-  if (dtype == GG_F32)
-    gg_launch(delta_conv_state_kernel<float>, sgrid, dim3(128), 0, stream, (const float*)x, x_stride, conv_state, cu_q_lens, context_lens, state_slots, C, taps);
-  else
-    gg_launch(delta_conv_state_kernel<__nv_bfloat16>, sgrid, dim3(128), 0, stream, (const __nv_bfloat16*)x, x_stride, conv_state, cu_q_lens, context_lens, state_slots, C, taps);
-  return gg_check_launch("delta_conv_state");
+  return conv_state_update(x, x_stride, dtype, conv_state, cu_q_lens, context_lens, state_slots, B, C, taps, stream);
 }
 
-template <int DPT>
+template <int DPT, bool CH, bool DELTA>
 static int delta_recur_launch(const float* qkv, const float* beta, const float* decay, float* state,
                               const int* cu_q_lens, const int* context_lens, const int* state_slots, int B, int G, int H,
                               int d, int dv, float* o_raw, cudaStream_t stream) {
   const int dp = DPT * DR_LANES;
-  const size_t smem = (size_t)(2 * DR_STAGE_FLOATS(dp) + DR_CHUNK * DR_COLS) * sizeof(float);
+  const size_t smem = (size_t)(2 * DR_STAGE_FLOATS_X(dp, CH) + DR_CHUNK * DR_COLS) * sizeof(float);
   if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(delta_recur_kernel<DPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(delta_recur_kernel<DPT, CH, DELTA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return gg_fail(GG_ERR_CUDA, "delta_recur: %s", cudaGetErrorString(e));
   }
   const dim3 grid(B, H, (dv + DR_COLS - 1) / DR_COLS);
-  gg_launch(delta_recur_kernel<DPT>, grid, dim3(DR_COLS * DR_LANES), smem, stream, qkv, beta, decay, state, cu_q_lens,
+  gg_launch(delta_recur_kernel<DPT, CH, DELTA>, grid, dim3(DR_COLS * DR_LANES), smem, stream, qkv, beta, decay, state, cu_q_lens,
             context_lens, state_slots, G, H, d, dv, o_raw);
   return gg_check_launch("delta_recur");
 }
 
 extern "C" int gg_delta_recur(const float* qkv, const float* beta, const float* decay, float* state,
                               const int* cu_q_lens, const int* context_lens, const int* state_slots, int B, int G, int H,
-                              int d, int dv, float* o_raw, cudaStream_t stream) {
+                              int d, int dv, int dw, int plain, float* o_raw, cudaStream_t stream) {
+  GG_REQUIRE(dw == 1 || dw == d, "delta_recur: a decay per head (1) or per key channel (%d), not %d", d, dw);
+  GG_REQUIRE(!plain || dw == 1, "delta_recur: the plain recurrence takes a decay per head");
   GG_REQUIRE(B > 0 && G > 0 && H > 0 && H % G == 0 && d > 0 && dv > 0, "delta_recur: bad sizes B=%d G=%d H=%d d=%d dv=%d", B, G, H, d, dv);
   GG_REQUIRE(d <= 256, "delta_recur: key size %d is beyond 256", d);
   GG_REQUIRE(H <= 65535 && (dv + DR_COLS - 1) / DR_COLS <= 65535, "delta_recur: too many heads or columns");
-#define DR_GO(N) return delta_recur_launch<N>(qkv, beta, decay, state, cu_q_lens, context_lens, state_slots, B, G, H, d, dv, o_raw, stream)
+#define DR_GO(N)                                                                                                              \
+  do {                                                                                                                        \
+    if (plain) return delta_recur_launch<N, false, false>(qkv, beta, decay, state, cu_q_lens, context_lens, state_slots, B, G, H, d, dv, o_raw, stream); \
+    if (dw > 1) return delta_recur_launch<N, true, true>(qkv, beta, decay, state, cu_q_lens, context_lens, state_slots, B, G, H, d, dv, o_raw, stream); \
+    return delta_recur_launch<N, false, true>(qkv, beta, decay, state, cu_q_lens, context_lens, state_slots, B, G, H, d, dv, o_raw, stream);            \
+  } while (0)
   if (d <= 16) DR_GO(2);
   if (d <= 32) DR_GO(4);
   if (d <= 64) DR_GO(8);
@@ -336,15 +384,16 @@ extern "C" int gg_delta_recur(const float* qkv, const float* beta, const float* 
 }
 
 extern "C" int gg_delta_out(const float* o_raw, const void* gate, long long gate_stride, int dtype, const float* w,
-                            float eps, int T, int H, int dv, void* out, cudaStream_t stream) {
+                            float eps, int T, int H, int dv, int gate_act, void* out, cudaStream_t stream) {
   GG_REQUIRE(T >= 0 && H > 0 && dv > 0 && H <= 65535, "delta_out: bad sizes T=%d H=%d dv=%d", T, H, dv);
+  GG_REQUIRE(gate_act == 0 || gate_act == 1, "delta_out: the gate passes silu (0) or a sigmoid (1), not %d", gate_act);
   if (T == 0) return GG_OK;
   const int threads = dv >= 256 ? 256 : (dv >= 128 ? 128 : 64);
   const dim3 grid(T, H);
   if (dtype == GG_F32)
-    gg_launch(delta_out_kernel<float>, grid, dim3(threads), 0, stream, o_raw, (const float*)gate, gate_stride, w, eps, H, dv, (float*)out);
+    gg_launch(delta_out_kernel<float>, grid, dim3(threads), 0, stream, o_raw, (const float*)gate, gate_stride, w, eps, H, dv, gate_act, (float*)out);
   else if (dtype == GG_BF16)
-    gg_launch(delta_out_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, o_raw, (const __nv_bfloat16*)gate, gate_stride, w, eps, H, dv, (__nv_bfloat16*)out);
+    gg_launch(delta_out_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, o_raw, (const __nv_bfloat16*)gate, gate_stride, w, eps, H, dv, gate_act, (__nv_bfloat16*)out);
   else
     return gg_fail(GG_ERR_INVALID, "delta_out: unknown dtype %d", dtype);
   return gg_check_launch("delta_out");

@@ -214,3 +214,160 @@ extern "C" int gg_diff_combine(const float* a, void* out, float lambda, float ep
   else return gg_fail(GG_ERR_INVALID, "diff_combine: unknown dtype %d", dtype);
   return gg_check_launch("diff_combine");
 }
+
+// ---------------------------------------------------------------- weighted sum of branches
+// out[t, :] = sum_i coef_i * y_i[t, :]
+struct SumArgs {
+  const void* y[MIX_MAX];
+  float coef[MIX_MAX];
+  int n;
+};
+
+template <typename TA>
+__global__ void weighted_sum_kernel(SumArgs m, long long n, TA* __restrict__ out) {
+  pdl_trigger();
+  pdl_wait();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    float v = 0.f;
+    for (int j = 0; j < m.n; ++j) v = fmaf(m.coef[j], to_f32(((const TA*)m.y[j])[i]), v);
+    out[i] = from_f32<TA>(v);
+  }
+}
+
+extern "C" int gg_weighted_sum(const void* const* ys, const float* coefs, int n, int T, int W, int dtype, void* out,
+                               cudaStream_t stream) {
+  GG_REQUIRE(n >= 1 && n <= MIX_MAX && T >= 0 && W > 0, "weighted_sum: bad sizes n=%d T=%d W=%d", n, T, W);
+  if (T == 0) return GG_OK;
+  SumArgs m = {};
+  m.n = n;
+  for (int i = 0; i < n; ++i) { m.y[i] = ys[i]; m.coef[i] = coefs[i]; }
+  const long long total = (long long)T * W;
+  const int blocks = (int)((total + 255) / 256 < 4096 ? (total + 255) / 256 : 4096);
+  if (dtype == GG_F32) gg_launch(weighted_sum_kernel<float>, dim3(blocks), dim3(256), 0, stream, m, total, (float*)out);
+  else if (dtype == GG_BF16) gg_launch(weighted_sum_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, m, total, (__nv_bfloat16*)out);
+  else return gg_fail(GG_ERR_INVALID, "weighted_sum: unknown dtype %d", dtype);
+  return gg_check_launch("weighted_sum");
+}
+
+// ---------------------------------------------------------------- token shift
+// out[t] = h[t] + (h[t - 1] - h[t]) * mu, the row before the first token of a step's portion taken
+// from the request's state slot (zeros at the start of the sequence); afterwards the slot holds the
+// portion's last row.  grid (T): only the block of a portion's first row touches the slot, and every
+// thread reads its columns of it before it writes them.
+template <typename TA>
+__global__ void token_shift_kernel(const TA* __restrict__ h, const float* __restrict__ mu, float* __restrict__ state,
+                                   const int* __restrict__ cu_q_lens, const int* __restrict__ context_lens,
+                                   const int* __restrict__ state_slots, int B, int W, TA* __restrict__ out) {
+  pdl_trigger();
+  const int t = blockIdx.x;
+  int lo = 0, hi = B - 1;
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (cu_q_lens[mid] <= t) lo = mid; else hi = mid - 1;
+  }
+  const int b = lo, t0 = cu_q_lens[b], qlen = cu_q_lens[b + 1] - t0;
+  const int slot = state_slots[b];
+  const int start = context_lens[b] - qlen;
+  pdl_wait();
+  const TA* cur = h + (size_t)t * W;
+  TA* o = out + (size_t)t * W;
+  if (t > t0) {
+    const TA* prev = cur - W;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+      const float x = to_f32(cur[c]);
+      o[c] = from_f32<TA>(fmaf(to_f32(prev[c]) - x, mu[c], x));
+    }
+    return;
+  }
+  float* st = slot >= 0 ? state + (size_t)slot * W : nullptr;
+  const TA* last = h + (size_t)(t0 + qlen - 1) * W;
+  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    const float x = to_f32(cur[c]);
+    const float p = (st && start > 0) ? st[c] : 0.f;
+    o[c] = from_f32<TA>(fmaf(p - x, mu[c], x));
+    if (st) st[c] = to_f32(last[c]);
+  }
+}
+
+extern "C" int gg_token_shift(const void* h, const float* mu, float* state, const int* cu_q_lens, const int* context_lens,
+                              const int* state_slots, int T, int B, int W, int dtype, void* out, cudaStream_t stream) {
+  GG_REQUIRE(T >= 0 && B > 0 && W > 0 && h && mu && state && out, "token_shift: bad arguments T=%d B=%d W=%d", T, B, W);
+  if (T == 0) return GG_OK;
+  const int threads = W >= 1024 ? 256 : 128;
+  if (dtype == GG_F32) gg_launch(token_shift_kernel<float>, dim3(T), dim3(threads), 0, stream, (const float*)h, mu, state, cu_q_lens, context_lens, state_slots, B, W, (float*)out);
+  else if (dtype == GG_BF16) gg_launch(token_shift_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, (const __nv_bfloat16*)h, mu, state, cu_q_lens, context_lens, state_slots, B, W, (__nv_bfloat16*)out);
+  else return gg_fail(GG_ERR_INVALID, "token_shift: unknown dtype %d", dtype);
+  return gg_check_launch("token_shift");
+}
+
+// ---------------------------------------------------------------- capped logits
+// x <- cap * tanh(x / cap), float32, in place
+__global__ void softcap_kernel(float* __restrict__ x, long long n, float cap, float inv) {
+  pdl_trigger();
+  pdl_wait();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    x[i] = cap * tanhf(x[i] * inv);
+}
+
+extern "C" int gg_softcap(float* x, long long n, float cap, cudaStream_t stream) {
+  GG_REQUIRE(n >= 0 && cap > 0.f && x, "softcap: bad arguments n=%lld cap=%g", n, (double)cap);
+  if (n == 0) return GG_OK;
+  const int blocks = (int)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096);
+  gg_launch(softcap_kernel, dim3(blocks), dim3(256), 0, stream, x, n, cap, 1.f / cap);
+  return gg_check_launch("softcap");
+}
+
+// ---------------------------------------------------------------- scaled embedding + learned positions
+// resid[t, :] = resid[t, :] * scale + table[positions[t], :]; a position past the table sets the flag
+template <typename TA>
+__global__ void scale_add_rows_kernel(float* __restrict__ resid, float scale, const TA* __restrict__ table,
+                                      const int* __restrict__ positions, int W, int rows, int* __restrict__ bad) {
+  pdl_trigger();
+  const int t = blockIdx.x;
+  int p = positions[t];
+  pdl_wait();
+  if (p < 0 || p >= rows) {
+    if (bad && threadIdx.x == 0) *bad = 1;
+    p = p < 0 ? 0 : rows - 1;
+  }
+  float* x = resid + (size_t)t * W;
+  const TA* r = table + (size_t)p * W;
+  for (int c = threadIdx.x; c < W; c += blockDim.x) x[c] = fmaf(x[c], scale, to_f32(r[c]));
+}
+
+extern "C" int gg_scale_add_rows(float* resid, float scale, const void* table, const int* positions, int T, int W,
+                                 int rows, int dtype, int* bad, cudaStream_t stream) {
+  GG_REQUIRE(T >= 0 && W > 0 && rows > 0 && resid && table && positions, "scale_add_rows: bad arguments T=%d W=%d rows=%d", T, W, rows);
+  if (T == 0) return GG_OK;
+  const int threads = W >= 1024 ? 256 : 128;
+  if (dtype == GG_F32) gg_launch(scale_add_rows_kernel<float>, dim3(T), dim3(threads), 0, stream, resid, scale, (const float*)table, positions, W, rows, bad);
+  else if (dtype == GG_BF16) gg_launch(scale_add_rows_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, resid, scale, (const __nv_bfloat16*)table, positions, W, rows, bad);
+  else return gg_fail(GG_ERR_INVALID, "scale_add_rows: unknown dtype %d", dtype);
+  return gg_check_launch("scale_add_rows");
+}
+
+// ---------------------------------------------------------------- elementwise sigmoid gate
+// out[t, c] = a[t, c] * sigmoid(g[t, c]); a float32 [T, W], g rows of stride g_stride in the activation type
+template <typename TA>
+__global__ void sigmoid_gate_kernel(const float* __restrict__ a, const TA* __restrict__ g, long long g_stride,
+                                    TA* __restrict__ out, long long n, int W) {
+  pdl_trigger();
+  pdl_wait();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / W;
+    const float z = to_f32(g[t * g_stride + (i - t * W)]);
+    out[i] = from_f32<TA>(a[i] / (1.f + expf(-z)));
+  }
+}
+
+extern "C" int gg_sigmoid_gate(const float* a, const void* g, long long g_stride, void* out, int T, int W, int dtype,
+                               cudaStream_t stream) {
+  GG_REQUIRE(T >= 0 && W > 0 && a && g && out && g_stride >= W, "sigmoid_gate: bad arguments T=%d W=%d", T, W);
+  if (T == 0) return GG_OK;
+  const long long n = (long long)T * W;
+  const int blocks = (int)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096);
+  if (dtype == GG_F32) gg_launch(sigmoid_gate_kernel<float>, dim3(blocks), dim3(256), 0, stream, a, (const float*)g, g_stride, (float*)out, n, W);
+  else if (dtype == GG_BF16) gg_launch(sigmoid_gate_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, a, (const __nv_bfloat16*)g, g_stride, (__nv_bfloat16*)out, n, W);
+  else return gg_fail(GG_ERR_INVALID, "sigmoid_gate: unknown dtype %d", dtype);
+  return gg_check_launch("sigmoid_gate");
+}

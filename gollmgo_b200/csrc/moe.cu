@@ -2,7 +2,9 @@
 // how many tokens an expert got, so a step of decoded tokens can be captured and replayed).
 //
 // gg_moe_route:   z[t, e] = h[t] . Wr[e] + b[e] in float32; the `top` largest logits of a token
-//                 (ties: the lower index) are its experts, weights = softmax over those alone
+//                 (ties: the lower index) are its experts, weights = softmax over those alone, or
+//                 the softmax over all experts renormalised over the chosen; optionally only
+//                 experts of the best groups can be chosen (moe_pick)
 // gg_moe_align:   the (token, choice) pairs sorted by expert: offsets[e] .. offsets[e+1] are the
 //                 places of expert e in `sorted` (values t * top + j), `place` is the inverse
 // gg_moe_combine: out[t] = sum_j weight[t, j] * y[place[t * top + j]] (+ shared[t]), float32 sums
@@ -31,9 +33,88 @@ __device__ __forceinline__ void route_load(const __nv_bfloat16* w, float (&v)[8]
   (void)n;
 }
 
+// One warp picks a token's experts from its logits zr[E] (shared memory, overwritten) and weighs them.
+// weigh = 0: weights = softmax over the chosen logits alone.  weigh = 1: scores = softmax over all
+// experts, weights = the chosen scores divided by their sum (+ 1e-20).  groups > 1: the experts form
+// that many equal groups of neighbours, a group's score is its best expert's, and only experts of the
+// `keep` best groups can be chosen.  Ties: the lower index.
+__device__ __forceinline__ void moe_pick(float* zr, int E, int top, int weigh, int groups, int keep, int lane,
+                                         int* __restrict__ idx, float* __restrict__ wgt) {
+  float zmax = 0.f, zsum = 1.f;
+  if (weigh == 1) {
+    float m = -INFINITY;
+    for (int e = lane; e < E; e += 32) m = fmaxf(m, zr[e]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    float sm = 0.f;
+    for (int e = lane; e < E; e += 32) sm += expf(zr[e] - m);
+    zmax = m; zsum = warp_sum(sm);
+  }
+  if (groups > 1 && keep < groups) {
+    const int per = E / groups;
+    unsigned kept = 0;                             // bit i: group lane + 32 i is kept
+    for (int k = 0; k < keep; ++k) {
+      float best = -INFINITY;
+      int bg = 0x7fffffff;
+      for (int g = lane, i = 0; g < groups; g += 32, ++i) {
+        if (kept >> i & 1u) continue;
+        float gm = -INFINITY;
+        for (int e = g * per; e < (g + 1) * per; ++e) gm = fmaxf(gm, zr[e]);
+        if (gm > best || (gm == best && g < bg)) { best = gm; bg = g; }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int og = __shfl_xor_sync(0xffffffffu, bg, o);
+        if (ov > best || (ov == best && og < bg)) { best = ov; bg = og; }
+      }
+      if (bg == 0x7fffffff) break;                 // nothing but NaN left
+      if ((bg & 31) == lane) kept |= 1u << (bg >> 5);
+    }
+    for (int e0 = 0; e0 < E; e0 += 32) {
+      const int e = e0 + lane, g = e < E ? e / per : 0;
+      const unsigned owner = __shfl_sync(0xffffffffu, kept, g & 31);
+      if (e < E && !(owner >> (g >> 5) & 1u)) zr[e] = -INFINITY;
+    }
+    __syncwarp();
+  }
+  float val[MOE_MAX_TOP];
+  for (int j = 0; j < top; ++j) {
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      const float v = zr[e];
+      if (v > best || (v == best && e < bi)) { best = v; bi = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if (bi == 0x7fffffff) bi = 0;                    // every logit left is -inf or NaN
+    val[j] = best;
+    if (lane == 0) { idx[j] = bi; zr[bi] = -INFINITY; }
+    __syncwarp();
+  }
+  if (lane == 0) {
+    if (weigh == 1) {
+      float sum = 0.f;
+      for (int j = 0; j < top; ++j) { val[j] = expf(val[j] - zmax) / zsum; sum += val[j]; }
+      for (int j = 0; j < top; ++j) wgt[j] = val[j] / (sum + 1e-20f);
+    } else {
+      const float m = val[0];                        // the largest comes first
+      float sum = 0.f;
+      for (int j = 0; j < top; ++j) { val[j] = expf(val[j] - m); sum += val[j]; }
+      for (int j = 0; j < top; ++j) wgt[j] = val[j] / sum;
+    }
+  }
+}
+
 template <typename TA, int TOK>
 __global__ void moe_route_kernel(const TA* __restrict__ h, const TA* __restrict__ wr, const float* __restrict__ bias,
-                                 int T, int D, int E, int top, int* __restrict__ idx, float* __restrict__ wgt, int vec) {
+                                 int T, int D, int E, int top, int weigh, int groups, int keep,
+                                 int* __restrict__ idx, float* __restrict__ wgt, int vec) {
   __shared__ float z[TOK][MOE_MAX_EXPERTS];
   extern __shared__ __align__(16) float xs[];              // TOK rows of D floats
   constexpr int VPT = 16 / (int)sizeof(TA);
@@ -79,41 +160,14 @@ __global__ void moe_route_kernel(const TA* __restrict__ h, const TA* __restrict_
     }
   }
   __syncthreads();
-  if (warp < nt) {                                         // warp r picks for token t0 + r (the block has TOK warps or more)
-    const int t = t0 + warp;
-    float* zr = z[warp];
-    float val[MOE_MAX_TOP];
-    for (int j = 0; j < top; ++j) {
-      float best = -INFINITY;
-      int bi = 0x7fffffff;
-      for (int e = lane; e < E; e += 32) {
-        const float v = zr[e];
-        if (v > best || (v == best && e < bi)) { best = v; bi = e; }
-      }
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
-      }
-      if (bi == 0x7fffffff) bi = 0;                  // every logit left is -inf or NaN
-      val[j] = best;
-      if (lane == 0) { idx[(size_t)t * top + j] = bi; zr[bi] = -INFINITY; }
-      __syncwarp();
-    }
-    if (lane == 0) {
-      const float m = val[0];                        // the largest comes first
-      float sum = 0.f;
-      for (int j = 0; j < top; ++j) { val[j] = expf(val[j] - m); sum += val[j]; }
-      for (int j = 0; j < top; ++j) wgt[(size_t)t * top + j] = val[j] / sum;
-    }
-  }
+  if (warp < nt)                                           // warp r picks for token t0 + r (the block has TOK warps or more)
+    moe_pick(z[warp], E, top, weigh, groups, keep, lane, idx + (size_t)(t0 + warp) * top, wgt + (size_t)(t0 + warp) * top);
 }
 
 // The choice alone, from logits a product has already made (long steps: z = h Wr^T in float32 by the
 // vendor library from the bfloat16 rows): one warp a token adds the bias, picks and weighs.
 __global__ void moe_topk_kernel(const float* __restrict__ z, const float* __restrict__ bias, int T, int E, int top,
-                                int* __restrict__ idx, float* __restrict__ wgt) {
+                                int weigh, int groups, int keep, int* __restrict__ idx, float* __restrict__ wgt) {
   extern __shared__ float zs[];                            // warps x E
   pdl_trigger();
   pdl_wait();
@@ -123,31 +177,7 @@ __global__ void moe_topk_kernel(const float* __restrict__ z, const float* __rest
   float* zr = zs + warp * E;
   for (int e = lane; e < E; e += 32) zr[e] = z[(size_t)t * E + e] + (bias ? bias[e] : 0.f);
   __syncwarp();
-  float val[MOE_MAX_TOP];
-  for (int j = 0; j < top; ++j) {
-    float best = -INFINITY;
-    int bi = 0x7fffffff;
-    for (int e = lane; e < E; e += 32) {
-      const float v = zr[e];
-      if (v > best || (v == best && e < bi)) { best = v; bi = e; }
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
-    }
-    if (bi == 0x7fffffff) bi = 0;
-    val[j] = best;
-    if (lane == 0) { idx[(size_t)t * top + j] = bi; zr[bi] = -INFINITY; }
-    __syncwarp();
-  }
-  if (lane == 0) {
-    const float m = val[0];
-    float sum = 0.f;
-    for (int j = 0; j < top; ++j) { val[j] = expf(val[j] - m); sum += val[j]; }
-    for (int j = 0; j < top; ++j) wgt[(size_t)t * top + j] = val[j] / sum;
-  }
+  moe_pick(zr, E, top, weigh, groups, keep, lane, idx + (size_t)t * top, wgt + (size_t)t * top);
 }
 
 // One CTA.  counts and cursors in shared memory; the order of the rows inside an expert's range
@@ -250,12 +280,20 @@ __global__ void moe_combine_kernel(const TA* __restrict__ y, const int* __restri
   }
 }
 
+static int check_pick(const char* who, int E, int top, int weigh, int groups, int keep) {
+  GG_REQUIRE(weigh == 0 || weigh == 1, "%s: unknown way %d of weighing the chosen experts", who, weigh);
+  GG_REQUIRE(groups >= 1 && keep >= 1 && keep <= groups && E % groups == 0, "%s: %d experts in %d groups of which %d are kept", who, E, groups, keep);
+  GG_REQUIRE(top <= keep * (E / groups), "%s: %d choices from %d groups of %d experts", who, top, keep, E / groups);
+  return GG_OK;
+}
+
 extern "C" int gg_moe_route(const void* h, const void* wr, const float* bias, int T, int D, int E, int top,
-                            int* idx, float* wgt, int act_dtype, cudaStream_t stream) {
+                            int weigh, int groups, int keep, int* idx, float* wgt, int act_dtype, cudaStream_t stream) {
   GG_REQUIRE(T >= 0 && D > 0 && E > 0 && top > 0 && top <= E, "moe_route: bad sizes T=%d D=%d E=%d top=%d", T, D, E, top);
   GG_REQUIRE(E <= MOE_MAX_EXPERTS && top <= MOE_MAX_TOP, "moe_route: at most %d experts and %d choices a token (got %d, %d)",
              MOE_MAX_EXPERTS, MOE_MAX_TOP, E, top);
   GG_REQUIRE(h && wr && idx && wgt, "moe_route: a pointer is null");
+  if (int rc = check_pick("moe_route", E, top, weigh, groups, keep)) return rc;
   if (T == 0) return GG_OK;
   const int tok = T > 256 ? ROUTE_TOK : 1;
   const size_t smem = (size_t)tok * D * sizeof(float);
@@ -266,7 +304,7 @@ extern "C" int gg_moe_route(const void* h, const void* wr, const float* bias, in
 #define ROUTE_LAUNCH(T_, N_)                                                                                     \
   do {                                                                                                           \
     if (smem > 28 * 1024) cudaFuncSetAttribute(moe_route_kernel<T_, N_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-    gg_launch(moe_route_kernel<T_, N_>, dim3(blocks), dim3(threads), smem, stream, (const T_*)h, (const T_*)wr, bias, T, D, E, top, idx, wgt, vec); \
+    gg_launch(moe_route_kernel<T_, N_>, dim3(blocks), dim3(threads), smem, stream, (const T_*)h, (const T_*)wr, bias, T, D, E, top, weigh, groups, keep, idx, wgt, vec); \
   } while (0)
   if (act_dtype == GG_F32) {
     if (tok == 1) ROUTE_LAUNCH(float, 1); else ROUTE_LAUNCH(float, ROUTE_TOK);
@@ -277,15 +315,16 @@ extern "C" int gg_moe_route(const void* h, const void* wr, const float* bias, in
   return gg_check_launch("moe_route");
 }
 
-extern "C" int gg_moe_topk(const float* z, const float* bias, int T, int E, int top, int* idx, float* wgt,
-                           cudaStream_t stream) {
+extern "C" int gg_moe_topk(const float* z, const float* bias, int T, int E, int top, int weigh, int groups, int keep,
+                           int* idx, float* wgt, cudaStream_t stream) {
   GG_REQUIRE(T >= 0 && E > 0 && top > 0 && top <= E && E <= MOE_MAX_EXPERTS && top <= MOE_MAX_TOP,
              "moe_topk: bad sizes T=%d E=%d top=%d", T, E, top);
   GG_REQUIRE(z && idx && wgt, "moe_topk: a pointer is null");
+  if (int rc = check_pick("moe_topk", E, top, weigh, groups, keep)) return rc;
   if (T == 0) return GG_OK;
   const int warps = 4;
   gg_launch(moe_topk_kernel, dim3((T + warps - 1) / warps), dim3(32 * warps), (size_t)warps * E * sizeof(float), stream,
-            z, bias, T, E, top, idx, wgt);
+            z, bias, T, E, top, weigh, groups, keep, idx, wgt);
   return gg_check_launch("moe_topk");
 }
 

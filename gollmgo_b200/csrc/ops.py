@@ -611,25 +611,33 @@ def head_gate(a: torch.Tensor, gates: torch.Tensor, col0: int, heads: int) -> No
 MOE_MAX_EXPERTS, MOE_MAX_TOP = 1024, 32
 
 
+MOE_WEIGH = {"softmax_chosen": 0, "softmax_all": 1}
+
+
 def moe_route(h: torch.Tensor, w_router: torch.Tensor, bias: Optional[torch.Tensor], top: int,
-              idx: torch.Tensor, wgt: torch.Tensor) -> None:
+              idx: torch.Tensor, wgt: torch.Tensor, weigh: str = "softmax_chosen", groups: int = 1, keep: int = 1) -> None:
     """Float32 logits h @ w_router^T + bias; idx [T, top] int32 = the largest, wgt [T, top]
-    float32 = softmax over those."""
+    float32 = softmax over those ("softmax_chosen"), or the softmax over all experts divided by the
+    chosen ones' sum ("softmax_all").  ``groups`` > 1: only experts of the ``keep`` groups (of
+    neighbouring experts) with the best expert can be chosen."""
     _cuda(h, w_router, bias, idx, wgt)
     T, D = h.shape
     E = w_router.shape[0]
     if w_router.dtype != h.dtype or w_router.shape[1] != D or idx.dtype != torch.int32 or wgt.dtype != torch.float32 \
             or (bias is not None and bias.dtype != torch.float32):
         raise KernelError("moe_route: router of the rows' dtype, bias and weights float32, choices int32")
-    _check(lib().gg_moe_route(_p(h), _p(w_router), _p(bias), T, D, E, top, _p(idx), _p(wgt), dtype_code(h.dtype), _stream()))
+    _check(lib().gg_moe_route(_p(h), _p(w_router), _p(bias), T, D, E, top, MOE_WEIGH[weigh], int(groups), int(keep),
+                               _p(idx), _p(wgt), dtype_code(h.dtype), _stream()))
 
 
-def moe_topk(z: torch.Tensor, bias: Optional[torch.Tensor], top: int, idx: torch.Tensor, wgt: torch.Tensor) -> None:
+def moe_topk(z: torch.Tensor, bias: Optional[torch.Tensor], top: int, idx: torch.Tensor, wgt: torch.Tensor,
+             weigh: str = "softmax_chosen", groups: int = 1, keep: int = 1) -> None:
     """moe_route's choice from logits z [T, E] (float32) that a product has already made."""
     _cuda(z, bias, idx, wgt)
     if z.dtype != torch.float32 or idx.dtype != torch.int32 or wgt.dtype != torch.float32:
         raise KernelError("moe_topk: logits and weights float32, choices int32")
-    _check(lib().gg_moe_topk(_p(z), _p(bias), z.shape[0], z.shape[1], top, _p(idx), _p(wgt), _stream()))
+    _check(lib().gg_moe_topk(_p(z), _p(bias), z.shape[0], z.shape[1], top, MOE_WEIGH[weigh], int(groups), int(keep),
+                              _p(idx), _p(wgt), _stream()))
 
 
 def moe_align(idx: torch.Tensor, n: int, experts: int, offsets: torch.Tensor, order: torch.Tensor,
@@ -707,25 +715,45 @@ def attn_prefill_x(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache:
                    tile_seq: torch.Tensor, tile_q0: torch.Tensor, num_tiles: int, out: torch.Tensor, nh: int, nkv: int,
                    d: int, dv: int, v_share: int, page_size: int, window: int, scale: float, softcap: float,
                    tile64_seq: Optional[torch.Tensor] = None, tile64_q0: Optional[torch.Tensor] = None,
-                   num_tiles64: int = 0, allow_mma: bool = True) -> None:
+                   num_tiles64: int = 0, allow_mma: bool = True, keep_first: int = 0, sigmoid_weights: bool = False,
+                   head_bias: Optional[torch.Tensor] = None, dist_bias: Optional[torch.Tensor] = None,
+                   dist_bucket: Optional[torch.Tensor] = None) -> None:
     """Causal attention of prompt portions with keys of size d, values of size dv, ``v_share`` key
     heads to a value head, optional window and capped scores; out [T, nh*dv] in the cache's type or
     float32.  ``tile_*`` list tiles of 16 queries (general kernel, float32 arithmetic), ``tile64_*``
-    of 64 (mma.sync kernel: bfloat16, d and dv 64 or 128)."""
+    of 64 (mma.sync kernel: bfloat16, d and dv 64 or 128).  General kernel only: ``keep_first`` keys at
+    the start of the sequence stay visible behind the window; ``dist_bias`` [rows, nh] float32 adds
+    row dist_bucket[min(i - j, len(dist_bucket) - 1)] to the scaled score of query i and key j;
+    ``sigmoid_weights``: a visible key weighs sigmoid(score + head_bias[h]) and nothing is normalised."""
+    _attn_extras(nh, head_bias, dist_bias, dist_bucket)
     _check(lib().gg_attn_prefill_x(_p(q), ctypes.c_longlong(q_stride), _p(kcache), _p(vcache), dtype_code(kcache.dtype),
                                    _p(block_tables), bt_stride, _p(cu_q_lens), _p(context_lens), _p(tile_seq),
                                    _p(tile_q0), num_tiles, _p(tile64_seq), _p(tile64_q0), num_tiles64, int(allow_mma),
                                    _p(out), int(out.dtype == torch.float32 and kcache.dtype != torch.float32),
                                    nh, nkv, d, dv, v_share, page_size, window, ctypes.c_float(scale),
-                                   ctypes.c_float(softcap), _stream()))
+                                   ctypes.c_float(softcap), int(keep_first), int(sigmoid_weights), _p(head_bias),
+                                   _p(dist_bias), _p(dist_bucket),
+                                   dist_bucket.numel() - 1 if dist_bucket is not None else 0, _stream()))
+
+
+def _attn_extras(nh, head_bias, dist_bias, dist_bucket) -> None:
+    _cuda(head_bias, dist_bias, dist_bucket)
+    if head_bias is not None and (head_bias.dtype != torch.float32 or head_bias.numel() != nh):
+        raise KernelError("attention: the bias per head is float32 [heads]")
+    if dist_bias is not None and (dist_bias.dtype != torch.float32 or dist_bias.dim() != 2 or dist_bias.shape[1] != nh
+                                  or dist_bucket is None or dist_bucket.dtype != torch.int32 or dist_bucket.numel() < 1):
+        raise KernelError("attention: the distance bias is float32 [rows, heads] with an int32 bucket table")
 
 
 def attn_decode_x(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache: torch.Tensor,
                   block_tables: torch.Tensor, bt_stride: int, cu_q_lens: torch.Tensor, context_lens: torch.Tensor,
                   dec_seqs: torch.Tensor, n_dec: int, num_splits: int, part_o: torch.Tensor, part_ml: torch.Tensor,
                   out: torch.Tensor, nh: int, nkv: int, d: int, dv: int, v_share: int, page_size: int, window: int,
-                  scale: float, softcap: float, allow_mma: bool = True) -> None:
+                  scale: float, softcap: float, allow_mma: bool = True, keep_first: int = 0,
+                  sigmoid_weights: bool = False, head_bias: Optional[torch.Tensor] = None,
+                  dist_bias: Optional[torch.Tensor] = None, dist_bucket: Optional[torch.Tensor] = None) -> None:
     """The same for single decoded tokens, split over the context and merged."""
+    _attn_extras(nh, head_bias, dist_bias, dist_bucket)
     if part_o.numel() < n_dec * nh * num_splits * dv or part_ml.numel() < n_dec * nh * num_splits * 2:
         raise KernelError("attn_decode_x: scratch too small")
     _check(lib().gg_attn_decode_x(_p(q), ctypes.c_longlong(q_stride), _p(kcache), _p(vcache), dtype_code(kcache.dtype),
@@ -733,7 +761,9 @@ def attn_decode_x(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache: 
                                   num_splits, _p(part_o), _p(part_ml), _p(out),
                                   int(out.dtype == torch.float32 and kcache.dtype != torch.float32), nh, nkv, d, dv,
                                   v_share, page_size, window, ctypes.c_float(scale), ctypes.c_float(softcap),
-                                  int(allow_mma), _stream()), 2)
+                                  int(allow_mma), int(keep_first), int(sigmoid_weights), _p(head_bias), _p(dist_bias),
+                                  _p(dist_bucket), dist_bucket.numel() - 1 if dist_bucket is not None else 0,
+                                  _stream()), 2)
 
 
 def diff_combine(maps: torch.Tensor, out: torch.Tensor, lam: float, eps: float, post: float, heads: int,
@@ -803,43 +833,139 @@ def clamped_gate(gate_up: torch.Tensor, out: torch.Tensor, limit: float, alpha: 
 
 
 # ---------------------------------------------------------------- gated delta rule
-def delta_prep(x: torch.Tensor, conv_w: torch.Tensor, conv_state: torch.Tensor, ba: torch.Tensor, a_log: torch.Tensor,
-               dt_bias: torch.Tensor, cu_q_lens: torch.Tensor, context_lens: torch.Tensor, state_slots: torch.Tensor,
-               num_seqs: int, kv_heads: int, heads: int, d: int, dv: int, qkv_out: torch.Tensor, beta: torch.Tensor,
-               decay: torch.Tensor) -> None:
+def delta_prep(x: torch.Tensor, conv_w: torch.Tensor, conv_state: torch.Tensor, zb: torch.Tensor, za: torch.Tensor,
+               a_log: torch.Tensor, dt_bias: torch.Tensor, cu_q_lens: torch.Tensor, context_lens: torch.Tensor,
+               state_slots: torch.Tensor, num_seqs: int, kv_heads: int, heads: int, d: int, dv: int,
+               qkv_out: torch.Tensor, beta: torch.Tensor, decay: torch.Tensor) -> None:
     """Short convolution + SiLU of the q, k, v channels of x [T, >= C] (C = 2*kv_heads*d + heads*dv)
     with the window carried in conv_state [slots, taps-1, C]; q and k made unit vectors (q times
-    d^-1/2); beta = sigmoid(ba[:, :H]), decay = exp(-exp(a_log) * softplus(ba[:, H:] + dt_bias)).
-    Then the window is moved on.  Outputs float32."""
-    _cuda(conv_w, conv_state, ba, a_log, dt_bias, qkv_out, beta, decay)
+    d^-1/2); beta = sigmoid(zb) [T, H], decay = exp(-exp(a_log) * softplus(za + dt_bias)) where za and
+    decay are [T, H] (a decay per head) or [T, H * d] (per head and key channel; dt_bias then [H * d]).
+    zb and za may be column views of one float32 buffer.  Then the window is moved on.  Outputs float32."""
+    _cuda(conv_w, conv_state, a_log, dt_bias, qkv_out, beta, decay)
     C, taps = conv_w.shape
     if x.stride(1) != 1 or C != 2 * kv_heads * d + heads * dv or conv_w.dtype != torch.float32 \
-            or conv_state.dtype != torch.float32 or ba.dtype != torch.float32 or qkv_out.dtype != torch.float32:
+            or conv_state.dtype != torch.float32 or zb.dtype != torch.float32 or za.dtype != torch.float32 \
+            or qkv_out.dtype != torch.float32 or zb.stride(1) != 1 or za.stride(1) != 1 or zb.shape[1] != heads:
         raise KernelError("delta_prep: bad shapes or dtypes")
+    dw = za.shape[1] // heads
+    if za.shape[1] != heads * dw or dt_bias.numel() != heads * dw or decay.numel() != x.shape[0] * heads * dw:
+        raise KernelError("delta_prep: the decay's input, bias and output disagree in width")
     _check(lib().gg_delta_prep(_p(x), ctypes.c_longlong(x.stride(0)), dtype_code(x.dtype), _p(conv_w), _p(conv_state),
-                               _p(ba), _p(a_log), _p(dt_bias), _p(cu_q_lens), _p(context_lens), _p(state_slots),
+                               _p(zb), ctypes.c_longlong(zb.stride(0)), _p(za), ctypes.c_longlong(za.stride(0)), dw,
+                               _p(a_log), _p(dt_bias), _p(cu_q_lens), _p(context_lens), _p(state_slots),
                                x.shape[0], num_seqs, kv_heads, heads, d, dv, taps, _p(qkv_out), _p(beta), _p(decay),
                                _stream()), 2 if taps > 1 else 1)
 
 
 def delta_recur(qkv: torch.Tensor, beta: torch.Tensor, decay: torch.Tensor, state: torch.Tensor,
                 cu_q_lens: torch.Tensor, context_lens: torch.Tensor, state_slots: torch.Tensor, num_seqs: int,
-                kv_heads: int, heads: int, d: int, dv: int, o_raw: torch.Tensor) -> None:
+                kv_heads: int, heads: int, d: int, dv: int, o_raw: torch.Tensor, plain: bool = False) -> None:
     """The recurrence S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q over every sequence's
-    tokens of the step, from and to state [slots, heads, dv, d] float32."""
+    tokens of the step, from and to state [slots, heads, dv, d] float32.  decay [T, heads]: g is a
+    number per head; [T, heads * d]: a factor per key channel (row of S).  ``plain``: u = beta v (the
+    write does not look at the state: the recurrence of a state-space layer)."""
     _cuda(qkv, beta, decay, state, o_raw)
     if state.dtype != torch.float32 or tuple(state.shape[1:]) != (heads, dv, d):
         raise KernelError("delta_recur: state must be float32 [slots, heads, dv, d]")
+    dw = decay.shape[-1] // heads
     _check(lib().gg_delta_recur(_p(qkv), _p(beta), _p(decay), _p(state), _p(cu_q_lens), _p(context_lens),
-                                _p(state_slots), num_seqs, kv_heads, heads, d, dv, _p(o_raw), _stream()))
+                                _p(state_slots), num_seqs, kv_heads, heads, d, dv, dw, int(plain), _p(o_raw), _stream()))
 
 
 def delta_out(o_raw: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, heads: int, dv: int,
-              out: torch.Tensor) -> None:
-    """out[t, h] = o / sqrt(mean(o^2) + eps) * weight * silu(gate[t, h]); gate is a column view
-    [T, heads*dv] of the projection's output."""
+              out: torch.Tensor, gate_act: str = "silu") -> None:
+    """out[t, h] = o / sqrt(mean(o^2) + eps) * weight * act(gate[t, h]), act = silu or sigmoid; gate is
+    a column view [T, heads*dv] of a projection's output."""
     _cuda(o_raw, weight, out)
     if gate.stride(1) != 1 or gate.dtype != out.dtype or weight.dtype != torch.float32:
         raise KernelError("delta_out: gate rows contiguous and of the output's dtype, float32 weight")
     _check(lib().gg_delta_out(_p(o_raw), _p(gate), ctypes.c_longlong(gate.stride(0)), dtype_code(out.dtype), _p(weight),
-                              ctypes.c_float(eps), out.shape[0], heads, dv, _p(out), _stream()))
+                              ctypes.c_float(eps), out.shape[0], heads, dv, {"silu": 0, "sigmoid": 1}[gate_act],
+                              _p(out), _stream()))
+
+
+# ---------------------------------------------------------------- state-space layer
+def ssm_prep(proj: torch.Tensor, conv_w: torch.Tensor, conv_b: Optional[torch.Tensor], conv_state: Optional[torch.Tensor],
+             a_log: torch.Tensor, dt_bias: torch.Tensor, cu_q_lens: torch.Tensor, context_lens: torch.Tensor,
+             state_slots: torch.Tensor, num_seqs: int, heads: int, vdim: int, groups: int, state: int,
+             cbx: torch.Tensor, dt: torch.Tensor, decay: torch.Tensor) -> None:
+    """Rows [z | x | B | C | dt] of proj: short convolution (+ bias) and SiLU over the x, B, C channels
+    with the window carried in conv_state [slots, taps-1, channels]; cbx [T, channels] float32 gets them
+    in the order [C | B | x]; dt = softplus(dt + dt_bias), decay = exp(-exp(a_log) dt), both [T, heads]
+    float32.  Then the window is moved on."""
+    _cuda(conv_w, conv_b, conv_state, a_log, dt_bias, cbx, dt, decay)
+    Cc, taps = conv_w.shape
+    if proj.stride(1) != 1 or Cc != heads * vdim + 2 * groups * state or conv_w.dtype != torch.float32 \
+            or cbx.dtype != torch.float32 or dt.dtype != torch.float32 or decay.dtype != torch.float32 \
+            or (conv_state is not None and conv_state.dtype != torch.float32):
+        raise KernelError("ssm_prep: bad shapes or dtypes")
+    _check(lib().gg_ssm_prep(_p(proj), ctypes.c_longlong(proj.stride(0)), dtype_code(proj.dtype), _p(conv_w), _p(conv_b),
+                             _p(conv_state), _p(a_log), _p(dt_bias), _p(cu_q_lens), _p(context_lens), _p(state_slots),
+                             proj.shape[0], num_seqs, heads, vdim, groups, state, taps, _p(cbx), _p(dt), _p(decay),
+                             _stream()), 2 if taps > 1 else 1)
+
+
+def ssm_out(y_raw: torch.Tensor, cbx: torch.Tensor, x_col: int, z: torch.Tensor, D: torch.Tensor, weight: torch.Tensor,
+            eps: float, heads: int, vdim: int, parts: int, out: torch.Tensor) -> None:
+    """out = rms-normed in ``parts`` equal parts of ((y_raw + D[h] x) * silu(z)), times weight; x is
+    cbx[:, x_col:], z a column view [T, heads*vdim] of the projection's output."""
+    _cuda(y_raw, cbx, D, weight, out)
+    if z.stride(1) != 1 or z.dtype != out.dtype or weight.dtype != torch.float32 or D.dtype != torch.float32:
+        raise KernelError("ssm_out: gate rows contiguous and of the output's dtype, float32 weight and D")
+    _check(lib().gg_ssm_out(_p(y_raw), _p(cbx), int(x_col), cbx.shape[1], _p(z), ctypes.c_longlong(z.stride(0)),
+                            dtype_code(out.dtype), _p(D), _p(weight), ctypes.c_float(eps), out.shape[0], heads, vdim,
+                            int(parts), _p(out), _stream()))
+
+
+# ---------------------------------------------------------------- more small row kernels
+def weighted_sum(ys, coefs, out: torch.Tensor) -> None:
+    """out = sum_i coefs[i] * ys[i]; ys of out's shape and dtype."""
+    _cuda(out, *ys)
+    n = len(ys)
+    if n != len(coefs) or any(y.shape != out.shape or y.dtype != out.dtype for y in ys):
+        raise KernelError("weighted_sum: branches of the output's shape and dtype, a factor each")
+    yp = (ctypes.c_void_p * n)(*[y.data_ptr() for y in ys])
+    cf = (ctypes.c_float * n)(*[float(c) for c in coefs])
+    _check(lib().gg_weighted_sum(yp, cf, n, out.shape[0], out.shape[1], dtype_code(out.dtype), _p(out), _stream()))
+
+
+def token_shift(h: torch.Tensor, mu: torch.Tensor, state: torch.Tensor, cu_q_lens: torch.Tensor,
+                context_lens: torch.Tensor, state_slots: torch.Tensor, num_seqs: int, out: torch.Tensor) -> None:
+    """out[t] = h[t] + (h[t-1] - h[t]) * mu; the row before a portion's first comes from
+    state[slot] (float32 [slots, W]; zeros at the start of a sequence), which then takes the portion's last row."""
+    _cuda(h, mu, state, out)
+    T, W = h.shape
+    if out.shape != h.shape or out.dtype != h.dtype or mu.dtype != torch.float32 or mu.numel() != W \
+            or state.dtype != torch.float32 or state.shape[-1] != W:
+        raise KernelError("token_shift: rows and result of one shape and dtype, float32 factors and state of their width")
+    _check(lib().gg_token_shift(_p(h), _p(mu), _p(state), _p(cu_q_lens), _p(context_lens), _p(state_slots), T, num_seqs,
+                                W, dtype_code(h.dtype), _p(out), _stream()))
+
+
+def softcap(x: torch.Tensor, cap: float) -> None:
+    """x <- cap * tanh(x / cap) in place (float32)."""
+    _cuda(x)
+    if x.dtype != torch.float32:
+        raise KernelError("softcap: float32 values")
+    _check(lib().gg_softcap(_p(x), ctypes.c_longlong(x.numel()), ctypes.c_float(cap), _stream()))
+
+
+def scale_add_rows(resid: torch.Tensor, scale: float, table: torch.Tensor, positions: torch.Tensor,
+                   bad: Optional[torch.Tensor] = None) -> None:
+    """resid[t] = resid[t] * scale + table[positions[t]] (resid float32 [T, W], table [rows, W])."""
+    _cuda(resid, table, positions, bad)
+    T, W = resid.shape
+    if resid.dtype != torch.float32 or table.shape[1] != W or positions.dtype != torch.int32:
+        raise KernelError("scale_add_rows: float32 rows, a table of their width, int32 positions")
+    _check(lib().gg_scale_add_rows(_p(resid), ctypes.c_float(scale), _p(table), _p(positions), T, W, table.shape[0],
+                                   dtype_code(table.dtype), _p(bad), _stream()))
+
+
+def sigmoid_gate(a: torch.Tensor, gate: torch.Tensor, out: torch.Tensor) -> None:
+    """out = a * sigmoid(gate): a float32 [T, W], gate a column view [T, W] of the activation type, out of that type."""
+    _cuda(a, out)
+    if a.dtype != torch.float32 or gate.dtype != out.dtype or gate.stride(1) != 1 or gate.shape != a.shape or out.shape != a.shape:
+        raise KernelError("sigmoid_gate: float32 values, gate and result of the activation type and one shape")
+    _check(lib().gg_sigmoid_gate(_p(a), _p(gate), ctypes.c_longlong(gate.stride(0)), _p(out), a.shape[0], a.shape[1],
+                                 dtype_code(out.dtype), _stream()))

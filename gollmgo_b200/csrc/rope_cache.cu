@@ -256,7 +256,8 @@ extern "C" int gg_rope_kv_write_x(void* qkv, long long row_stride, int act_dtype
                                   const int* slot_mapping, const double* inv_freq, float mag, const float* bias,
                                   void* kcache, void* vcache, int T, int nh, int nkv, int d, int nv, int dv, int rot,
                                   int page_size, int interleaved, int write_cache, cudaStream_t stream) {
-  GG_REQUIRE(T >= 0 && nh > 0 && nkv > 0 && d > 0 && nv > 0 && dv > 0 && page_size > 0,
+  // nv = 0: the rows hold no values of their own (a layer whose values are its keys)
+  GG_REQUIRE(T >= 0 && nh > 0 && nkv > 0 && d > 0 && nv >= 0 && dv > 0 && page_size > 0,
              "rope_kv_write_x: bad sizes T=%d nh=%d nkv=%d d=%d nv=%d dv=%d page=%d", T, nh, nkv, d, nv, dv, page_size);
   GG_REQUIRE(rot >= 0 && rot <= d && rot % 2 == 0, "rope_kv_write_x: rotary width %d must be even and <= head size %d", rot, d);
   GG_REQUIRE(row_stride >= (long long)(nh + nkv) * d + (long long)nv * dv, "rope_kv_write_x: rows of %lld values are too short", row_stride);

@@ -31,7 +31,8 @@ def _prefixed(prefix: str, weights: Dict[str, WeightSpec], single_name: str = ""
     return {prefix + local: spec for local, spec in weights.items()}
 
 
-def spec_manifest(spec: ModelSpec, parts=None, embed_position=None, blocks=None, final_norm=None) -> Dict[str, WeightSpec]:
+def spec_manifest(spec: ModelSpec, parts=None, embed_position=None, blocks=None, final_norm=None,
+                  embed_norm=None) -> Dict[str, WeightSpec]:
     """Checkpoint tensors the model expects.  ``parts`` = per layer
     (mixer, feed_forward, mixer_norm, ffn_norm) if already built; ``blocks`` = the layers' blocks
     (one that has tensors of its own offers ``weights()`` and ``load(get)``)."""
@@ -53,6 +54,8 @@ def spec_manifest(spec: ModelSpec, parts=None, embed_position=None, blocks=None,
         m[spec.final_norm_name] = WeightSpec((spec.hidden_size,))
     if embed_position is not None:
         m.update(_prefixed(spec.embed_position_prefix, embed_position.weights()))
+    if embed_norm is not None:
+        m.update(_prefixed("", embed_norm.weights(), spec.embed_norm_name))
     if spec.input_mix_name:
         m[spec.input_mix_name] = WeightSpec((spec.hidden_size, 2 * spec.hidden_size))
     m[spec.head_name] = WeightSpec((spec.vocab_size, spec.hidden_size), optional=spec.tie_embeddings)
@@ -74,6 +77,9 @@ class DecoderModel:
             self.blocks.append(build_block(ls, mixer, ff, n1, n2, ctx))
         self.final_norm = build_norm(spec.final_norm, ctx)
         self.embed_position = build_position(spec.embed_position, ctx) if spec.embed_position else None
+        self.embed_norm = build_norm(spec.embed_norm, ctx) if spec.embed_norm else None
+        if self.embed_norm is not None and not hasattr(self.embed_norm, "norm_in_place"):
+            raise TypeError(f"norm {type(self.embed_norm).__name__} cannot sit on the embedding output (no norm_in_place)")
         ws = ctx.workspace
         ws.reserve("residual", ctx.max_tokens * spec.hidden_size, torch.float32)
         ws.reserve("head_in", ctx.max_tokens * spec.hidden_size, ctx.act_dtype)
@@ -91,7 +97,7 @@ class DecoderModel:
 
     # ------------------------------------------------------------------ weights
     def manifest(self) -> Dict[str, WeightSpec]:
-        return spec_manifest(self.spec, self.parts, self.embed_position, self.blocks, self.final_norm)
+        return spec_manifest(self.spec, self.parts, self.embed_position, self.blocks, self.final_norm, self.embed_norm)
 
     def load(self, get: Callable[[str], torch.Tensor]) -> None:
         """Bind weights: ``get(name)`` delivers a checkpoint tensor on the device."""
@@ -111,6 +117,8 @@ class DecoderModel:
         self.final_norm.load(lambda local: get(s.final_norm_name + local))
         if self.embed_position is not None:
             self.embed_position.load(lambda local, p=s.embed_position_prefix: get(p + local))
+        if self.embed_norm is not None:
+            self.embed_norm.load(lambda local: get(s.embed_norm_name + local))
         if self.mixes_input:
             self.w_input_mix = get(s.input_mix_name).contiguous()
         head = None if s.tie_embeddings else get(s.head_name)
@@ -124,6 +132,7 @@ class DecoderModel:
                 seen.add(t.data_ptr())
                 total += t.numel() * t.element_size()
         add(self.embed), add(self.head), add(self.w_input_mix)
+        add(getattr(self.embed_position, "table", None))
         def add_part(part, depth=0):
             for v in vars(part).values():
                 if isinstance(v, torch.Tensor) and v.dim() >= 1 and v.is_cuda:
@@ -185,8 +194,16 @@ class DecoderModel:
         resid = ws.get("residual", T, H)
         ops.embed_gather(batch.token_ids, self.embed, resid, self.bad_id,
                          getattr(batch, "token_src", None), getattr(batch, "prev_tokens", None))
+        scale = float(self.spec.embed_scale)
         if self.embed_position is not None:
-            self.embed_position.add_to_embedding(resid, batch)
+            if scale != 1.0:
+                self.embed_position.add_to_embedding(resid, batch, scale=scale)     # scale and positions in one pass
+            else:
+                self.embed_position.add_to_embedding(resid, batch)
+        elif scale != 1.0:
+            resid.mul_(scale)
+        if self.embed_norm is not None:
+            self.embed_norm.norm_in_place(resid)
         delta = None
         order = self.spec.run_order
         x0 = None
@@ -219,6 +236,8 @@ class DecoderModel:
             delta = None                       # the last block has added everything to the residual itself
         self.final_norm.add_norm(resid, delta, h, rows=batch.logit_rows, write_back=False)
         linear(h, self.head, logits)
+        if self.spec.logit_softcap > 0:
+            ops.softcap(logits, float(self.spec.logit_softcap))
         return logits
 
 

@@ -10,9 +10,17 @@ steps in bfloat16 take the tcgen05 product of csrc/gemm_tc.cu over rows gathered
 per expert), and a last kernel sums each token's results in float32.  No count ever reaches the host, so a step of
 decoded tokens is captured like any other.
 
-params: hidden_size, intermediate_size, experts, top, router_bias (bool), shared (a feed-forward
-PartSpec or None), names: dict with "router", "router_bias", "expert" (a format string with
-{e}), "gate", "up", "down", "shared" (prefix of the shared expert's tensors).
+Variants, all parameters: ``router_weigh="softmax_all"``: the scores are the softmax over all
+experts and the weights the chosen scores divided by their sum (+ 1e-20); ``groups`` = (count, keep):
+the experts form ``count`` equal groups of neighbours, a group's score is its best expert's, and
+only experts of the ``keep`` best groups can be chosen; ``activation="clamped_swish"`` (``limit``,
+``alpha`` = 1.702, ``shift`` = 1): an expert computes g * sigmoid(alpha g) * (u + shift) with
+g = min(gate, limit), u = clamp(up, -limit, limit) instead of silu(gate) * up.
+
+params: hidden_size, intermediate_size, experts, top, router_bias (bool), router_weigh, groups,
+activation, limit, alpha, shift, shared (a feed-forward PartSpec or None), names: dict with "router",
+"router_bias", "expert" (a format string with {e}), "gate", "up", "down", "shared" (prefix of the
+shared expert's tensors).
 """
 from __future__ import annotations
 
@@ -51,6 +59,21 @@ class MixtureOfExperts:
             raise ValueError(f"the routing kernels take at most {ops.MOE_MAX_EXPERTS} experts and "
                              f"{ops.MOE_MAX_TOP} choices a token")
         self.router_bias = bool(spec.get("router_bias", True))
+        self.weigh = spec.get("router_weigh") or "softmax_chosen"
+        if self.weigh not in ops.MOE_WEIGH:
+            raise ValueError(f"router weights {self.weigh!r} are not known (known: {sorted(ops.MOE_WEIGH)})")
+        self.group_count, self.group_keep = (int(g) for g in (spec.get("groups") or (1, 1)))
+        if self.experts % self.group_count or not (1 <= self.group_keep <= self.group_count) \
+                or self.top > self.group_keep * (self.experts // self.group_count):
+            raise ValueError(f"{self.experts} experts in {self.group_count} groups of which {self.group_keep} are kept "
+                             f"do not give {self.top} choices")
+        self.activation = spec.get("activation") or "silu"
+        if self.activation not in ("silu", "clamped_swish"):
+            raise ValueError(f"activation {self.activation!r} is not supported (known: silu, clamped_swish)")
+        if self.activation == "clamped_swish":
+            self.limit = float(spec["limit"])
+            self.alpha = float(spec.get("alpha", 1.702))
+            self.shift = float(spec.get("shift", 1.0))
         self.names = {**DEFAULT_NAMES, **(spec.get("names") or {})}
         shared = spec.get("shared")
         self.shared = build_feed_forward(shared, ctx) if shared is not None else None
@@ -68,6 +91,8 @@ class MixtureOfExperts:
         ws.reserve("moe_tiles", slots // TC_TILE + 1, torch.int32)
         ws.reserve("moe_in", slots * self.hidden, ctx.act_dtype)
         ws.reserve("moe_act", slots * self.inter, ctx.act_dtype)
+        if self.activation != "silu":
+            ws.reserve("moe_gate_up", slots * 2 * self.inter, ctx.act_dtype)
         ws.reserve("moe_rows", slots * self.hidden, ctx.act_dtype)
         ws.reserve("moe_out", T * self.hidden, ctx.act_dtype)
         self.w_router = self.b_router = self.w_gate_up = self.w_down = None
@@ -109,10 +134,14 @@ class MixtureOfExperts:
             # a long step: the logits are a product like any other (bfloat16 rows, float32 sums and result)
             z = ws.get("moe_logits", T, self.experts)
             linear(x, self.w_router, z)
-            ops.moe_topk(z, self.b_router, self.top, idx, wgt)
+            ops.moe_topk(z, self.b_router, self.top, idx, wgt, self.weigh, self.group_count, self.group_keep)
         else:
-            ops.moe_route(x, self.w_router, self.b_router, self.top, idx, wgt)
+            ops.moe_route(x, self.w_router, self.b_router, self.top, idx, wgt, self.weigh, self.group_count,
+                          self.group_keep)
         return idx, wgt
+
+    def _activate(self, gate_up, a):
+        ops.clamped_gate(gate_up, a, self.limit, self.alpha, self.shift)
 
     def forward(self, x, batch):
         T, ws = x.shape[0], self.ctx.workspace
@@ -128,15 +157,26 @@ class MixtureOfExperts:
             xin = ws.get("moe_in", slots, self.hidden)
             ops.moe_gather(x, order, self.top, xin)
             a = ws.get("moe_act", slots, self.inter)
-            ops.gemm_tc_grouped(xin, self.w_gate_up, a, tiles, E, gated=True)
+            if self.activation == "silu":
+                ops.gemm_tc_grouped(xin, self.w_gate_up, a, tiles, E, gated=True)
+            else:
+                gu = ws.get("moe_gate_up", slots, 2 * self.inter)
+                ops.gemm_tc_grouped(xin, self.w_gate_up, gu, tiles, E)
+                self._activate(gu, a)
             y = ws.get("moe_rows", slots, self.hidden)
             ops.gemm_tc_grouped(a, self.w_down, y, tiles, E)
         else:
             order = ws.get("moe_order", 1, n)
             ops.moe_align(idx, n, E, offsets, order, place)
             a = ws.get("moe_act", n, self.inter)
-            ops.grouped_gemm(x, self.w_gate_up, a, self.inter, self.hidden, E, offsets=offsets, row_index=order,
-                             row_div=self.top, rows=n, gated=True)
+            if self.activation == "silu":
+                ops.grouped_gemm(x, self.w_gate_up, a, self.inter, self.hidden, E, offsets=offsets, row_index=order,
+                                 row_div=self.top, rows=n, gated=True)
+            else:
+                gu = ws.get("moe_gate_up", n, 2 * self.inter)
+                ops.grouped_gemm(x, self.w_gate_up, gu, 2 * self.inter, self.hidden, E, offsets=offsets, row_index=order,
+                                 row_div=self.top, rows=n)
+                self._activate(gu, a)
             y = ws.get("moe_rows", n, self.hidden)
             ops.grouped_gemm(a, self.w_down, y, self.hidden, self.inter, E, offsets=offsets, rows=n)
         shared = self.shared.forward(x, batch) if self.shared is not None else None

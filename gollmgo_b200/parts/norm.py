@@ -15,17 +15,27 @@ from .registry import register_norm
 
 
 class RMSNorm:
+    """params: size, eps, scalar (bool: the weight is one number for all coordinates; the kernels then
+    get it repeated ``size`` times)."""
+
     def __init__(self, spec, ctx):
         self.size = int(spec["size"])
         self.eps = float(spec["eps"])
+        self.scalar = bool(spec.get("scalar", False))
         self.ctx = ctx
         self.weight = None
 
     def weights(self):
-        return {"": WeightSpec((self.size,))}
+        return {"": WeightSpec(() if self.scalar else (self.size,))}
 
     def load(self, get):
-        self.weight = get("").to(torch.float32).contiguous()
+        w = get("").to(torch.float32)
+        self.weight = (w.reshape(1).expand(self.size) if self.scalar else w).contiguous()
+
+    def norm_in_place(self, resid):
+        """resid <- norm(resid) * weight, float32 rows (the kernel holds a row in shared memory before it
+        writes any of it)."""
+        ops.add_rmsnorm(resid, None, self.weight, resid, self.eps, None, False)
 
     def rms_weight_eps(self):
         """(weight, eps) for a product that folds this norm in (parts/linear.py): only a norm

@@ -13,6 +13,8 @@ from dataclasses import dataclass
 
 import torch
 
+from ..csrc import ops
+from ..weights import WeightSpec
 from .registry import register_position
 
 
@@ -90,5 +92,31 @@ class NoPositionEncoding:
         return None
 
 
+class LearnedPositions:
+    """A table of learned position vectors that is added to the embedded tokens (named in
+    ``ModelSpec.embed_position``): x <- x * scale + table[position].  params: hidden_size,
+    max_positions.  Its one tensor: "" (the prefix alone), [max_positions, hidden_size]."""
+    interleaved = False
+
+    def __init__(self, spec, ctx):
+        self.hidden = int(spec["hidden_size"])
+        self.max_positions = int(spec["max_positions"])
+        self.table = None
+        self.bad = torch.zeros(1, dtype=torch.int32, device=ctx.device) if ctx.device.type == "cuda" else None
+
+    def rope_table(self):
+        return None
+
+    def weights(self):
+        return {"": WeightSpec((self.max_positions, self.hidden))}
+
+    def load(self, get):
+        self.table = get("").contiguous()
+
+    def add_to_embedding(self, resid, batch, scale: float = 1.0):
+        ops.scale_add_rows(resid, scale, self.table, batch.positions, self.bad)
+
+
+register_position("learned", LearnedPositions)
 register_position("rope", RotaryEncoding)
 register_position("none", NoPositionEncoding)

@@ -85,6 +85,13 @@ class ModelSpec:
     # the tensor of the run entries' mix_input (a model that runs some of its layers several
     # times feeds the embedding output back in at the start of every pass); "" = none
     input_mix_name: str = ""
+    # the embedded tokens are multiplied by this before anything else is done with them
+    embed_scale: float = 1.0
+    # a norm on the embedding output (after the scale and an ``embed_position``), with its tensor's name
+    embed_norm: Optional[PartSpec] = None
+    embed_norm_name: str = ""
+    # > 0: logits <- cap * tanh(logits / cap)
+    logit_softcap: float = 0.0
 
     @property
     def num_cache_entries(self) -> int:

@@ -48,6 +48,8 @@ class WeightSpec:
     optional: bool = False       # may be absent (e.g. lm_head of a tied model)
     init: str = ""               # how random weights are drawn where the shape does not say: "normal" (a
                                  # vector that is no norm weight), "taps" (rows of a short convolution)
+    free_dims: Tuple[int, ...] = ()   # dimensions whose size the checkpoint decides (``shape`` holds the size that
+                                      # random weights are made with); the part reads the size from the tensor
 
 
 # Tensors some exporters add that carry no parameters of the model.
@@ -73,7 +75,8 @@ def check_manifest(manifest: Dict[str, WeightSpec], found: Dict[str, Tuple[Tuple
     for n, s in manifest.items():
         if n in found:
             shape, dt = found[n]
-            if tuple(shape) != tuple(s.shape):
+            if len(shape) != len(s.shape) or any(a != b for i, (a, b) in enumerate(zip(shape, s.shape))
+                                                 if i not in s.free_dims):
                 wrong_shape.append((n, shape, s.shape))
             if s.kind == "float" and not dt.is_floating_point:
                 wrong_dtype.append((n, dt))

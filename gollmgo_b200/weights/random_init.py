@@ -32,7 +32,7 @@ def random_tensor(name: str, spec: WeightSpec, seed: int, device, dtype: torch.d
         t.normal_(0.0, 1.0 / spec.shape[-1], generator=gen)
         t[..., -1] += 1.0
         return t.to(dtype)
-    if len(spec.shape) == 1 and spec.init != "normal":      # a norm's weight
+    if len(spec.shape) <= 1 and spec.init != "normal":      # a norm's weight (a vector, or one number)
         t = torch.ones(spec.shape, dtype=torch.float32, device=device)
         if norm_jitter:
             t += norm_jitter * torch.randn(spec.shape, generator=gen, dtype=torch.float32, device=device)
