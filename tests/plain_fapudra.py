@@ -50,7 +50,7 @@ def token_shift(h, mu):
 
 # ---------------------------------------------------------------- state-space mixer
 def mamba2(h, w, p, m, eps):
-    H, P, N, G = m["heads"], m["vdim"], m["state"], m["groups"]
+    H, P, N, G = m["heads"], m["vdim"], m["state"], m.get("groups", 1)
     inner = H * P
     T = h.shape[0]
     proj = h @ w[p + "in"].T
@@ -62,14 +62,13 @@ def mamba2(h, w, p, m, eps):
     dt = softplus(dt + w[p + "dt_bias"][None, :])
     rate = np.exp(w[p + "A_log"])
     y = np.zeros((T, H, P))
-    for hd in range(H):
-        g = hd // (H // G)
-        S = np.zeros((N, P))
-        for t in range(T):
-            S = math.exp(-rate[hd] * dt[t, hd]) * S + dt[t, hd] * np.outer(Bm[t, g], x[t, hd])
-            y[t, hd] = S.T @ Cm[t, g] + w[p + "D"][hd] * x[t, hd]
+    group_of = np.arange(H) // (H // G)
+    S = np.zeros((H, N, P))                                    # one state matrix per head
+    for t in range(T):
+        S = np.exp(-rate * dt[t])[:, None, None] * S + dt[t][:, None, None] * Bm[t, group_of][:, :, None] * x[t][:, None, :]
+        y[t] = np.einsum("hnp,hn->hp", S, Cm[t, group_of]) + w[p + "D"][:, None] * x[t]
     y = y.reshape(T, inner) * silu(z)
-    parts = m["norm_groups"]
+    parts = m.get("norm_groups", 1)
     y = unit_rms(y.reshape(T, parts, inner // parts), eps).reshape(T, inner) * w[p + "norm"][None, :]
     return y @ w[p + "o"].T
 
@@ -89,15 +88,16 @@ def sigmoid_attention(h, w, p, m):
     k = (h @ w[p + "k"].T + w[p + "k.b"]).reshape(T, G, d)
     rel = w[p + "rel"]
     rows, far = rel.shape[0], m["bias_max"]
-    size, first = m["mask"]["size"], m["mask"]["keep_first"]
+    mask = m.get("mask") or {}
+    size, first = mask.get("size"), mask.get("keep_first", 0)
+    i, j = np.arange(T)[:, None], np.arange(T)[None, :]
+    seen = (j <= i) & ((i - j < size) | (j < first)) if size else (j <= i)
+    bucket = np.array([distance_bucket(n, rows, far) for n in range(T)])[np.maximum(i - j, 0)]
     out = np.zeros((T, H, d))
     for hd in range(H):
         g = hd // (H // G)
-        for i in range(T):
-            for j in range(i + 1):
-                if i - j < size or j < first:
-                    s = float(q[i, hd] @ k[j, g]) * m["scale"] + rel[distance_bucket(i - j, rows, far), hd]
-                    out[i, hd] += sigmoid(s + w[p + "pb"][hd]) * k[j, g]
+        s = (q[:, hd] @ k[:, g].T) * m["scale"] + rel[bucket, hd] + w[p + "pb"][hd]
+        out[:, hd] = np.where(seen, sigmoid(s), 0.0) @ k[:, g]        # weights are not normalised over the keys
     out = out.reshape(T, H * d) * sigmoid(h @ w[p + "g"].T)
     return out @ w[p + "o"].T
 
@@ -115,35 +115,38 @@ def channel_delta_rule(h, w, p, m, eps):
     step = softplus((h @ w[p + "a1"].T) @ w[p + "a2"].T + w[p + "dt_bias"][None, :]).reshape(T, H, d)
     keep = np.exp(-np.exp(w[p + "A_log"])[None, :, None] * step)
     o = np.zeros((T, H, dv))
-    for hd in range(H):
-        g = hd // (H // G)
-        S = np.zeros((d, dv))
-        for t in range(T):
-            S = keep[t, hd][:, None] * S
-            u = beta[t, hd] * (v[t, hd] - S.T @ k[t, g])
-            S = S + np.outer(k[t, g], u)
-            o[t, hd] = S.T @ q[t, g]
+    group_of = np.arange(H) // (H // G)
+    S = np.zeros((H, d, dv))
+    for t in range(T):
+        kt, qt = k[t, group_of], q[t, group_of]
+        S = keep[t][:, :, None] * S
+        u = beta[t][:, None] * (v[t] - np.einsum("hdv,hd->hv", S, kt))
+        S = S + kt[:, :, None] * u[:, None, :]
+        o[t] = np.einsum("hdv,hd->hv", S, qt)                  # the read-out sees this token's write
     o = unit_rms(o, eps) * w[p + "norm"][None, None, :]
     o = o.reshape(T, H * dv) * sigmoid((h @ w[p + "g1"].T) @ w[p + "g2"].T)
     return o @ w[p + "o"].T
 
 
 def parallel_mixer(h, w, p, m, eps):
-    return (m["left_scale"] * sigmoid_attention(h, w, p + "left.", m["left"])
-            + m["right_scale"] * channel_delta_rule(h, w, p + "right.", m["right"], eps))
+    return (m.get("left_scale", 1.0) * sigmoid_attention(h, w, p + "left.", m["left"])
+            + m.get("right_scale", 1.0) * channel_delta_rule(h, w, p + "right.", m["right"], eps))
 
 
 # ---------------------------------------------------------------- mixture of experts
-def route(h, w_router, r):
+def route(h, w_router, r, gaps=None):
     """Per token the chosen experts and their weights: softmax over all experts; experts outside
-    the best ``keep`` groups (a group's score is its best expert's) cannot be chosen."""
+    the best ``keep`` groups (a group's score is its best expert's) cannot be chosen.  ``gaps``: a
+    list that receives, per token, how far (in logits) the closest call of the choice was."""
     z = h @ w_router.T
+    z0 = z
     z = z - z.max(axis=-1, keepdims=True)
     s = np.exp(z)
     s = s / s.sum(axis=-1, keepdims=True)
     E, top = r["experts"], r["top"]
-    count, keep = r["groups"]["count"], r["groups"]["keep"]
-    chosen, weights = [], []
+    grp = r.get("groups") or {"count": 1, "keep": 1}
+    count, keep = grp["count"], grp["keep"]
+    chosen, weights, margin = [], [], []
     for t in range(h.shape[0]):
         per = E // count
         best = np.array([s[t, g * per:(g + 1) * per].max() for g in range(count)])
@@ -151,9 +154,19 @@ def route(h, w_router, r):
         allowed = np.full(E, -np.inf)
         for g in groups:
             allowed[g * per:(g + 1) * per] = s[t, g * per:(g + 1) * per]
-        idx = np.argsort(-allowed, kind="stable")[:top]
+        order = np.argsort(-allowed, kind="stable")
+        idx = order[:top]
         chosen.append(idx)
         weights.append(s[t, idx] / (s[t, idx].sum() + 1e-20))
+        gap = np.inf
+        if keep < count:
+            gz = np.sort(np.array([z0[t, g * per:(g + 1) * per].max() for g in range(count)]))[::-1]
+            gap = min(gap, gz[keep - 1] - gz[keep])
+        if top < keep * per:
+            gap = min(gap, z0[t, order[top - 1]] - z0[t, order[top]])
+        margin.append(gap)
+    if gaps is not None:
+        gaps.append(np.array(margin))
     return np.array(chosen), np.array(weights)
 
 
@@ -163,8 +176,8 @@ def expert(h, w, p, limit):
     return (g * sigmoid(1.702 * g) * (u + 1.0)) @ w[p + "down"].T
 
 
-def mixture(h, w, p, f):
-    idx, wgt = route(h, w[p + "router"], f["router"])
+def mixture(h, w, p, f, gaps=None):
+    idx, wgt = route(h, w[p + "router"], f["router"], gaps)
     out = np.zeros_like(h)
     for t in range(h.shape[0]):
         for e, a in zip(idx[t], wgt[t]):
@@ -173,13 +186,14 @@ def mixture(h, w, p, f):
 
 
 # ---------------------------------------------------------------- the model
-def forward(cfg, w, tokens, layers_out=None):
+def forward(cfg, w, tokens, layers_out=None, gaps=None):
     """Logits [T, vocab] of one sequence.  ``layers_out``: a list that receives the residual
-    stream after every layer."""
+    stream after every layer; ``gaps``: a list that receives, per layer with experts, every token's
+    closest call in the choice of experts."""
     eps = cfg["norm"]["eps"]
     tokens = np.asarray(tokens)
     T = len(tokens)
-    x = w["embed"][tokens] * cfg["embedding"]["scale"] + w["pos"][:T]
+    x = w["embed"][tokens] * (cfg.get("embedding") or {}).get("scale", 1.0) + w["pos"][:T]
     x = unit_rms(x, eps) * w["embed.norm"]
     for i, layer in enumerate(cfg["layers"]):
         p = f"l{i}."
@@ -191,7 +205,7 @@ def forward(cfg, w, tokens, layers_out=None):
             a = parallel_mixer(hm, w, p + "mix.", layer["mixer"], eps)
         else:
             raise ValueError(layer["type"])
-        f = mixture(h, w, p + "mlp.", layer["mlp"]) if layer.get("mlp") else 0.0
+        f = mixture(h, w, p + "mlp.", layer["mlp"], gaps) if layer.get("mlp") else 0.0
         x = x + (a + f)
         if layers_out is not None:
             layers_out.append(x.copy())
