@@ -156,10 +156,13 @@ def reference_arm(args) -> int:
 # size.  Tekenex: a Llama decoder of equal width, depth, heads, head size and vocabulary with one
 # kv head (its cache rows are as wide as the latent's).  Bevuvik: a Llama decoder of equal width,
 # heads, kv heads, feed-forward width and vocabulary with as many layers as the Bevuvik shape runs
-# (the layers of its repeated run counted once per pass).
+# (the layers of its repeated run counted once per pass).  Fapudra: the Bevuvik shape of equal width,
+# heads, kv heads, head size and number of layer runs (it has the attention beside a delta rule and the
+# recurrent state; its dense feed-forward is as wide as the two experts a Fapudra token uses together).
 DESIGN_PAIRS = {
     "tekenex": [("tekenex_w2048", "llama_mqa_w2048"), ("tekenex_w4096", "llama_mqa_w4096")],
     "bevuvik": [("bevuvik_w2048", "llama_gqa_w2048"), ("bevuvik_w4096", "llama_gqa_w4096")],
+    "fapudra": [("fapudra_w2048", "bevuvik_w2048"), ("fapudra_w4096", "bevuvik_w4096")],
 }
 
 

@@ -128,5 +128,5 @@ def save_file(tensors: Iterable[Tuple[str, torch.Tensor]], path: str, metadata: 
         f.write(blob)
         for _, t in items:
             if t.numel():
-                f.write(t.view(torch.uint8).numpy().tobytes() if t.dtype != torch.bool
+                f.write(t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.dtype != torch.bool
                         else t.to(torch.uint8).numpy().tobytes())
