@@ -532,7 +532,8 @@ extern "C" int gg_attn_prefill_x(const void* q, long long q_stride, const void* 
   if (rc) return rc;
   GG_REQUIRE(weights == 0 || weights == 1, "attn_prefill_x: unknown kind of weights %d", weights);
   GG_REQUIRE(!dist_bias || (dist_bucket && dist_max >= 0), "attn_prefill_x: a distance bias needs its bucket table");
-  const bool plain = !a.keep_first && !weights && !head_bias && !dist_bias;   // what the mma.sync kernels compute
+  // what the mma.sync kernels compute: softmax without these extras, or sigmoid weights with all of them
+  const bool plain = (!a.keep_first && !weights && !head_bias && !dist_bias) || attn_mma_x_sigmoid_supported(a);
   // bfloat16 with sizes of 64 or 128: the mma.sync kernel over tiles of 64 queries
   if (plain && allow_mma && tile64_seq && attn_mma_x_supported(dtype, d, dv > 0 ? dv : d, page_size) && q_stride % 8 == 0) {
     a.tile_seq = tile64_seq; a.tile_q0 = tile64_q0;
@@ -561,7 +562,8 @@ extern "C" int gg_attn_decode_x(const void* q, long long q_stride, const void* k
   if (rc) return rc;
   GG_REQUIRE(weights == 0 || weights == 1, "attn_decode_x: unknown kind of weights %d", weights);
   GG_REQUIRE(!dist_bias || (dist_bucket && dist_max >= 0), "attn_decode_x: a distance bias needs its bucket table");
-  if (a.keep_first || weights || head_bias || dist_bias) allow_mma = 0;       // the general kernel has these
+  if ((a.keep_first || weights || head_bias || dist_bias) && !attn_mma_x_sigmoid_supported(a))
+    allow_mma = 0;                                                            // only the general kernel has these with softmax
   GG_REQUIRE(n_dec >= 0 && num_splits >= 1 && num_splits <= 65535, "attn_decode_x: bad n_dec %d or splits %d", n_dec, num_splits);
   GG_REQUIRE(part_o && part_ml, "attn_decode_x: no scratch given");
   if (n_dec == 0) return GG_OK;

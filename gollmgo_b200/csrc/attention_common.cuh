@@ -55,6 +55,9 @@ int attn_decode_cluster_capacity(int d, int splits, int group);
 // the same with values of another size than keys, shared value heads, capped scores, float32 out (a.dv, a.v_share, a.softcap, a.out_f32)
 bool attn_mma_x_supported(int dtype, int d, int dv, int page_size);
 int attn_prefill_mma_x(const AttnArgs& a, int num_tiles, cudaStream_t stream);   // tiles of 64 queries
+// a.weights == 1 (sigmoid weights, kept first keys, biases by head and distance) on the same kernels
+#define ATTN_MMA_X_MAX_DIST 16384      // entries of the distance table that fit in shared memory beside the tiles
+bool attn_mma_x_sigmoid_supported(const AttnArgs& a);
 int attn_decode_mma_x(const AttnArgs& a, int n_dec, cudaStream_t stream);        // partial results; the caller merges
 // large batches: the tiles of all (token, kv head) pairs cut into equal ranges, one per CTA
 int attn_decode_flat_ctas(int d);

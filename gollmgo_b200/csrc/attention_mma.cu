@@ -1061,7 +1061,17 @@ __device__ __forceinline__ float score_exp2(float dot, float scale, float cap, f
   return x * LOG2E;
 }
 
-template <int DK, int DV>
+// sigmoid(x) of a score in base e: one exponential and one reciprocal of the special-function unit
+__device__ __forceinline__ float sigmoid_weight(float x) {
+  return __fdividef(1.f, 1.f + fast_exp2(-x * LOG2E));
+}
+
+// SIG: every visible key weighs sigmoid(score + bias) by itself and nothing is normalised; the
+// bias of head h at distance n is dist_bias[dist_bucket[min(n, dist_max)], h] + head_bias[h], laid
+// out once per CTA as a table over distances behind the staged tiles; the first keep_first keys
+// stay visible behind the window (their tiles come first); where the values are the keys (one
+// cache tensor, equal sizes) the staged key tile serves as the value tile.
+template <int DK, int DV, bool SIG>
 __global__ void __launch_bounds__(MMA_THREADS) attn_prefill_mma_x_kernel(AttnArgs a) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   constexpr int K_BYTES = MMA_BK * DK * 2, V_BYTES = MMA_BK * DV * 2, STAGE = K_BYTES + V_BYTES;
@@ -1079,15 +1089,28 @@ __global__ void __launch_bounds__(MMA_THREADS) attn_prefill_mma_x_kernel(AttnArg
   const int hi = first + nrows;
   const int lo = a.window > 0 ? max(0, first - a.window + 1) : 0;
   const int kstart = (lo / MMA_BK) * MMA_BK;
-  const int ntiles = (hi - kstart + MMA_BK - 1) / MMA_BK;
+  const int first_hi = SIG ? min(a.keep_first, lo) : 0;            // kept first keys behind the window: [0, first_hi)
+  const int n0 = (first_hi + MMA_BK - 1) / MMA_BK;
+  const int ntiles = n0 + (hi - kstart + MMA_BK - 1) / MMA_BK;
   const int* bt = a.block_tables + (size_t)b * a.bt_stride;
   const __nv_bfloat16* kc = (const __nv_bfloat16*)a.kcache;
   const __nv_bfloat16* vc = (const __nv_bfloat16*)a.vcache;
+  const bool kv_same = SIG && DK == DV && vc == kc && nv == a.nkv;
   const unsigned base = smem_u32(smem_raw);
+  float* tab = reinterpret_cast<float*>(smem_raw + STAGES * STAGE);
+  if (SIG) {                                                        // weights of the model: nothing of this step
+    const float hb = a.head_bias ? a.head_bias[h] : 0.f;
+    for (int n = threadIdx.x; n <= a.dist_max; n += MMA_THREADS)
+      tab[n] = hb + (a.dist_bias ? a.dist_bias[(size_t)a.dist_bucket[n] * a.nh + h] : 0.f);
+  }
   pdl_wait();
+  // tile `it` starts at key tile_kb(it) and takes the keys of [tile_lo(it), tile_hi(it))
+  auto tile_kb = [&](int it) { return it < n0 ? it * MMA_BK : kstart + (it - n0) * MMA_BK; };
+  auto tile_lo = [&](int it) { return it < n0 ? 0 : lo; };
+  auto tile_hi = [&](int it) { return it < n0 ? first_hi : hi; };
 
-  load_tile_of<DK>(kc, a.nkv, kvh, bt, kstart, lo, hi, base, ps_log2);
-  load_tile_of<DV>(vc, nv, vh, bt, kstart, lo, hi, base + K_BYTES, ps_log2);
+  load_tile_of<DK>(kc, a.nkv, kvh, bt, tile_kb(0), tile_lo(0), tile_hi(0), base, ps_log2);
+  if (!kv_same) load_tile_of<DV>(vc, nv, vh, bt, tile_kb(0), tile_lo(0), tile_hi(0), base + K_BYTES, ps_log2);
   cp_async_commit();
 
   const int wrow0 = warp * 16;
@@ -1107,31 +1130,60 @@ __global__ void __launch_bounds__(MMA_THREADS) attn_prefill_mma_x_kernel(AttnArg
   for (int it = 0; it < ntiles; ++it) {
     if (it + 1 < ntiles) {
       const int st = (it + 1) % STAGES;
-      load_tile_of<DK>(kc, a.nkv, kvh, bt, kstart + (it + 1) * MMA_BK, lo, hi, base + st * STAGE, ps_log2);
-      load_tile_of<DV>(vc, nv, vh, bt, kstart + (it + 1) * MMA_BK, lo, hi, base + st * STAGE + K_BYTES, ps_log2);
+      load_tile_of<DK>(kc, a.nkv, kvh, bt, tile_kb(it + 1), tile_lo(it + 1), tile_hi(it + 1), base + st * STAGE, ps_log2);
+      if (!kv_same)
+        load_tile_of<DV>(vc, nv, vh, bt, tile_kb(it + 1), tile_lo(it + 1), tile_hi(it + 1), base + st * STAGE + K_BYTES, ps_log2);
     }
     cp_async_commit();
     cp_async_wait<STAGES - 1>();
     __syncthreads();
     const int st = it % STAGES;
-    const unsigned ks = base + st * STAGE, vs = ks + K_BYTES;
-    const int kb = kstart + it * MMA_BK;
+    const unsigned ks = base + st * STAGE, vs = kv_same ? ks : ks + K_BYTES;
+    const int kb = tile_kb(it), tlo = tile_lo(it), thi = tile_hi(it);
     if (wrow0 < nrows && kb <= wlast) {
       float s[8][4];
       qk_mma<DK, 8>(qf, ks, 0, s);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int tk = kb + j * 8 + c2 + (e & 1);
-          const int pos = (e & 2) ? pos1 : pos0;
-          const bool ok = ((e & 2) ? row1_ok : row0_ok) && tk >= lo && tk <= pos &&
-                          (a.window <= 0 || tk > pos - a.window);
-          s[j][e] = ok ? score_exp2(s[j][e], scale, cap, inv_cap) : -INFINITY;
-        }
-      }
       unsigned p[4][4];
-      softmax_update<DV, 8>(s, m, l, o, p);
+      if (SIG) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int tk = kb + j * 8 + c2 + (e & 1);
+            const int pos = (e & 2) ? pos1 : pos0;
+            const bool ok = ((e & 2) ? row1_ok : row0_ok) && tk >= tlo && tk < thi && tk <= pos &&
+                            (a.window <= 0 || tk > pos - a.window || tk < a.keep_first);
+            float x = s[j][e] * scale;
+            if (cap > 0.f) {
+              float th;
+              asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(x * inv_cap));
+              x = cap * th;
+            }
+            x += tab[min(max(pos - tk, 0), a.dist_max)];
+            s[j][e] = ok ? sigmoid_weight(x) : 0.f;
+          }
+        }
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+          p[kk][0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+          p[kk][1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+          p[kk][2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+          p[kk][3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int tk = kb + j * 8 + c2 + (e & 1);
+            const int pos = (e & 2) ? pos1 : pos0;
+            const bool ok = ((e & 2) ? row1_ok : row0_ok) && tk >= lo && tk <= pos &&
+                            (a.window <= 0 || tk > pos - a.window);
+            s[j][e] = ok ? score_exp2(s[j][e], scale, cap, inv_cap) : -INFINITY;
+          }
+        }
+        softmax_update<DV, 8>(s, m, l, o, p);
+      }
       pv_mma<DV, 8>(p, vs, 0, o);
     }
     __syncthreads();
@@ -1142,7 +1194,7 @@ __global__ void __launch_bounds__(MMA_THREADS) attn_prefill_mma_x_kernel(AttnArg
   l[0] += __shfl_xor_sync(0xffffffffu, l[0], 2);
   l[1] += __shfl_xor_sync(0xffffffffu, l[1], 1);
   l[1] += __shfl_xor_sync(0xffffffffu, l[1], 2);
-  const float inv0 = l[0] > 0.f ? 1.f / l[0] : 0.f, inv1 = l[1] > 0.f ? 1.f / l[1] : 0.f;
+  const float inv0 = SIG ? 1.f : l[0] > 0.f ? 1.f / l[0] : 0.f, inv1 = SIG ? 1.f : l[1] > 0.f ? 1.f / l[1] : 0.f;
   const size_t ostride = (size_t)a.nh * DV;
   const size_t at0 = (size_t)(t0 + q0 + wrow0 + g) * ostride + (size_t)h * DV, at1 = at0 + 8 * ostride;
 #pragma unroll
@@ -1160,7 +1212,9 @@ __global__ void __launch_bounds__(MMA_THREADS) attn_prefill_mma_x_kernel(AttnArg
   }
 }
 
-template <int DK, int DV>
+// SIG as in the prompt kernel; the slices' sums simply add up in the merge kernel, and the first
+// slice also takes the kept first keys behind the window.
+template <int DK, int DV, bool SIG>
 __global__ void __launch_bounds__(MMA_THREADS) attn_decode_mma_x_kernel(AttnArgs a) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   constexpr int K_BYTES = MMA_BK * DK * 2, V_BYTES = MMA_BK * DV * 2, STAGE = K_BYTES + V_BYTES;
@@ -1184,17 +1238,23 @@ __global__ void __launch_bounds__(MMA_THREADS) attn_decode_mma_x_kernel(AttnArgs
   const int* bt = a.block_tables + (size_t)(b >= 0 ? b : 0) * a.bt_stride;
   const __nv_bfloat16* kc = (const __nv_bfloat16*)a.kcache;
   const __nv_bfloat16* vc = (const __nv_bfloat16*)a.vcache;
+  const bool kv_same = SIG && DK == DV && vc == kc && nv == a.nkv;
   const unsigned base = smem_u32(smem_raw);
 
-  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float m[2] = {SIG ? 0.f : -INFINITY, SIG ? 0.f : -INFINITY}, l[2] = {SIG ? 1.f : 0.f, SIG ? 1.f : 0.f};
   float o[DV / 8][4];
 #pragma unroll
   for (int nt = 0; nt < DV / 8; ++nt) { o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f; }
-  const int ntiles = lo < hi ? (hi - lo + MMA_BK - 1) / MMA_BK : 0;
+  const int first_hi = SIG && split == 0 ? min(a.keep_first, lo0) : 0;     // kept first keys behind the window
+  const int n0 = (first_hi + MMA_BK - 1) / MMA_BK;
+  const int ntiles = n0 + (lo < hi ? (hi - lo + MMA_BK - 1) / MMA_BK : 0);
+  auto tile_kb = [&](int it) { return it < n0 ? it * MMA_BK : lo + (it - n0) * MMA_BK; };
+  auto tile_lo = [&](int it) { return it < n0 ? 0 : lo; };
+  auto tile_hi = [&](int it) { return it < n0 ? first_hi : hi; };
   pdl_wait();
   if (ntiles > 0) {
-    load_tile_of<DK>(kc, a.nkv, kvh, bt, lo, lo, hi, base, ps_log2);
-    load_tile_of<DV>(vc, nv, vh, bt, lo, lo, hi, base + K_BYTES, ps_log2);
+    load_tile_of<DK>(kc, a.nkv, kvh, bt, tile_kb(0), tile_lo(0), tile_hi(0), base, ps_log2);
+    if (!kv_same) load_tile_of<DV>(vc, nv, vh, bt, tile_kb(0), tile_lo(0), tile_hi(0), base + K_BYTES, ps_log2);
     cp_async_commit();
     unsigned qf[DK / 16][4];
     const __nv_bfloat16* qbase = (const __nv_bfloat16*)a.q + (size_t)t * a.q_stride + (size_t)head0 * DK;
@@ -1203,29 +1263,64 @@ __global__ void __launch_bounds__(MMA_THREADS) attn_decode_mma_x_kernel(AttnArgs
     for (int it = 0; it < ntiles; ++it) {
       if (it + 1 < ntiles) {
         const int st = (it + 1) % STAGES;
-        load_tile_of<DK>(kc, a.nkv, kvh, bt, lo + (it + 1) * MMA_BK, lo, hi, base + st * STAGE, ps_log2);
-        load_tile_of<DV>(vc, nv, vh, bt, lo + (it + 1) * MMA_BK, lo, hi, base + st * STAGE + K_BYTES, ps_log2);
+        load_tile_of<DK>(kc, a.nkv, kvh, bt, tile_kb(it + 1), tile_lo(it + 1), tile_hi(it + 1), base + st * STAGE, ps_log2);
+        if (!kv_same)
+          load_tile_of<DV>(vc, nv, vh, bt, tile_kb(it + 1), tile_lo(it + 1), tile_hi(it + 1), base + st * STAGE + K_BYTES, ps_log2);
       }
       cp_async_commit();
       cp_async_wait<STAGES - 1>();
       __syncthreads();
       const int st = it % STAGES;
-      const unsigned ks = base + st * STAGE, vs = ks + K_BYTES;
+      const unsigned ks = base + st * STAGE, vs = kv_same ? ks : ks + K_BYTES;
       const int key0 = warp * 16;
-      const int tok0 = lo + it * MMA_BK + key0;
-      if (tok0 < hi) {
+      const int tok0 = tile_kb(it) + key0, thi = tile_hi(it);
+      if (tok0 < thi) {
         float s[2][4];
         qk_mma<DK, 2>(qf, ks, key0, s);
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-          const int tk = tok0 + j * 8 + c2;
-          s[j][0] = tk < hi ? score_exp2(s[j][0], scale, cap, inv_cap) : -INFINITY;
-          s[j][2] = tk < hi ? score_exp2(s[j][2], scale, cap, inv_cap) : -INFINITY;
-          s[j][1] = tk + 1 < hi ? score_exp2(s[j][1], scale, cap, inv_cap) : -INFINITY;
-          s[j][3] = tk + 1 < hi ? score_exp2(s[j][3], scale, cap, inv_cap) : -INFINITY;
-        }
         unsigned p[1][4];
-        softmax_update<DV, 2>(s, m, l, o, p);
+        if (SIG) {
+          // rows g and g + 8 of the tile are heads head0 + g and head0 + g + 8 (clamped where the group is smaller)
+          const int hr0 = head0 + min(g, nrows - 1), hr1 = head0 + min(g + 8, nrows - 1);
+          const float hb0 = a.head_bias ? a.head_bias[hr0] : 0.f, hb1 = a.head_bias ? a.head_bias[hr1] : 0.f;
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const int tk = tok0 + j * 8 + c2 + e;
+              const bool ok = tk < thi;
+              float b0 = hb0, b1 = hb1;
+              if (ok && a.dist_bias) {
+                const size_t row = (size_t)a.dist_bucket[min(ctx - 1 - tk, a.dist_max)] * a.nh;
+                b0 += a.dist_bias[row + hr0];
+                b1 += a.dist_bias[row + hr1];
+              }
+              float x0 = s[j][e] * scale, x1 = s[j][2 + e] * scale;
+              if (cap > 0.f) {
+                float th;
+                asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(x0 * inv_cap));
+                x0 = cap * th;
+                asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(x1 * inv_cap));
+                x1 = cap * th;
+              }
+              s[j][e] = ok ? sigmoid_weight(x0 + b0) : 0.f;
+              s[j][2 + e] = ok ? sigmoid_weight(x1 + b1) : 0.f;
+            }
+          }
+          p[0][0] = pack_bf16(s[0][0], s[0][1]);
+          p[0][1] = pack_bf16(s[0][2], s[0][3]);
+          p[0][2] = pack_bf16(s[1][0], s[1][1]);
+          p[0][3] = pack_bf16(s[1][2], s[1][3]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            const int tk = tok0 + j * 8 + c2;
+            s[j][0] = tk < hi ? score_exp2(s[j][0], scale, cap, inv_cap) : -INFINITY;
+            s[j][2] = tk < hi ? score_exp2(s[j][2], scale, cap, inv_cap) : -INFINITY;
+            s[j][1] = tk + 1 < hi ? score_exp2(s[j][1], scale, cap, inv_cap) : -INFINITY;
+            s[j][3] = tk + 1 < hi ? score_exp2(s[j][3], scale, cap, inv_cap) : -INFINITY;
+          }
+          softmax_update<DV, 2>(s, m, l, o, p);
+        }
         pv_mma<DV, 2>(p, vs, key0, o);
       }
       __syncthreads();
@@ -1279,42 +1374,61 @@ bool attn_mma_x_supported(int dtype, int d, int dv, int page_size) {
   return dtype == GG_BF16 && (d == 64 || d == 128) && (dv == 64 || dv == 128) && power_of_two(page_size);
 }
 
-template <int DK, int DV>
+template <int DK, int DV, bool SIG>
 static int prefill_x_go(const AttnArgs& a, int num_tiles, cudaStream_t stream) {
-  const size_t smem = (size_t)2 * MMA_BK * (DK + DV) * 2;
-  int rc = opt_in_smem(attn_prefill_mma_x_kernel<DK, DV>, smem, "attn_prefill_x");
+  const size_t smem = (size_t)2 * MMA_BK * (DK + DV) * 2 + (SIG ? (size_t)(a.dist_max + 1) * sizeof(float) : 0);
+  int rc = opt_in_smem(attn_prefill_mma_x_kernel<DK, DV, SIG>, smem, "attn_prefill_x");
   if (rc) return rc;
-  gg_launch(attn_prefill_mma_x_kernel<DK, DV>, dim3(num_tiles, a.nh), dim3(MMA_THREADS), smem, stream, a);
+  gg_launch(attn_prefill_mma_x_kernel<DK, DV, SIG>, dim3(num_tiles, a.nh), dim3(MMA_THREADS), smem, stream, a);
   return gg_check_launch("attn_prefill_x");
+}
+
+// what the SIG kernels take: sigmoid weights (with or without the biases and kept first keys), and a
+// table over distances that fits beside the staged tiles
+bool attn_mma_x_sigmoid_supported(const AttnArgs& a) {
+  return a.weights == 1 && a.dist_max >= 0 && a.dist_max < ATTN_MMA_X_MAX_DIST && (!a.dist_bias || a.dist_bucket);
 }
 
 int attn_prefill_mma_x(const AttnArgs& a, int num_tiles, cudaStream_t stream) {
   GG_REQUIRE(num_tiles >= 0 && a.nh <= 65535, "attn_prefill_x: bad grid");
   if (num_tiles == 0) return GG_OK;
   const int dv = a.dv > 0 ? a.dv : a.d;
-  if (a.d == 64 && dv == 64) return prefill_x_go<64, 64>(a, num_tiles, stream);
-  if (a.d == 64 && dv == 128) return prefill_x_go<64, 128>(a, num_tiles, stream);
-  if (a.d == 128 && dv == 64) return prefill_x_go<128, 64>(a, num_tiles, stream);
-  return prefill_x_go<128, 128>(a, num_tiles, stream);
+  if (a.weights == 1) {
+    GG_REQUIRE(attn_mma_x_sigmoid_supported(a), "attn_prefill_x: a distance table of %d entries does not fit", a.dist_max + 1);
+    if (a.d == 64 && dv == 64) return prefill_x_go<64, 64, true>(a, num_tiles, stream);
+    if (a.d == 64 && dv == 128) return prefill_x_go<64, 128, true>(a, num_tiles, stream);
+    if (a.d == 128 && dv == 64) return prefill_x_go<128, 64, true>(a, num_tiles, stream);
+    return prefill_x_go<128, 128, true>(a, num_tiles, stream);
+  }
+  if (a.d == 64 && dv == 64) return prefill_x_go<64, 64, false>(a, num_tiles, stream);
+  if (a.d == 64 && dv == 128) return prefill_x_go<64, 128, false>(a, num_tiles, stream);
+  if (a.d == 128 && dv == 64) return prefill_x_go<128, 64, false>(a, num_tiles, stream);
+  return prefill_x_go<128, 128, false>(a, num_tiles, stream);
 }
 
-template <int DK, int DV>
+template <int DK, int DV, bool SIG>
 static int decode_x_go(const AttnArgs& a, int n_dec, cudaStream_t stream) {
   size_t smem = (size_t)2 * MMA_BK * (DK + DV) * 2;
   const size_t combine = (size_t)(128 + 4 * 16 * DV) * sizeof(float);
   if (combine > smem) smem = combine;
-  int rc = opt_in_smem(attn_decode_mma_x_kernel<DK, DV>, smem, "attn_decode_x");
+  int rc = opt_in_smem(attn_decode_mma_x_kernel<DK, DV, SIG>, smem, "attn_decode_x");
   if (rc) return rc;
   const int G = a.nh / a.nkv, gchunks = (G + 15) / 16;
   GG_REQUIRE(a.nkv * gchunks <= 65535 && a.num_splits <= 65535, "attn_decode_x: too many heads or slices");
-  gg_launch(attn_decode_mma_x_kernel<DK, DV>, dim3(n_dec, a.nkv * gchunks, a.num_splits), dim3(MMA_THREADS), smem, stream, a);
+  gg_launch(attn_decode_mma_x_kernel<DK, DV, SIG>, dim3(n_dec, a.nkv * gchunks, a.num_splits), dim3(MMA_THREADS), smem, stream, a);
   return gg_check_launch("attn_decode_x");
 }
 
 int attn_decode_mma_x(const AttnArgs& a, int n_dec, cudaStream_t stream) {
   const int dv = a.dv > 0 ? a.dv : a.d;
-  if (a.d == 64 && dv == 64) return decode_x_go<64, 64>(a, n_dec, stream);
-  if (a.d == 64 && dv == 128) return decode_x_go<64, 128>(a, n_dec, stream);
-  if (a.d == 128 && dv == 64) return decode_x_go<128, 64>(a, n_dec, stream);
-  return decode_x_go<128, 128>(a, n_dec, stream);
+  if (a.weights == 1) {
+    if (a.d == 64 && dv == 64) return decode_x_go<64, 64, true>(a, n_dec, stream);
+    if (a.d == 64 && dv == 128) return decode_x_go<64, 128, true>(a, n_dec, stream);
+    if (a.d == 128 && dv == 64) return decode_x_go<128, 64, true>(a, n_dec, stream);
+    return decode_x_go<128, 128, true>(a, n_dec, stream);
+  }
+  if (a.d == 64 && dv == 64) return decode_x_go<64, 64, false>(a, n_dec, stream);
+  if (a.d == 64 && dv == 128) return decode_x_go<64, 128, false>(a, n_dec, stream);
+  if (a.d == 128 && dv == 64) return decode_x_go<128, 64, false>(a, n_dec, stream);
+  return decode_x_go<128, 128, false>(a, n_dec, stream);
 }

@@ -710,6 +710,10 @@ def rope_kv_write_x(qkv: torch.Tensor, positions: torch.Tensor, slot_mapping: Op
                                     int(write_cache), _stream()))
 
 
+# distances whose bias the mma.sync kernels with sigmoid weights can tabulate in shared memory (attention_common.cuh)
+ATTN_MMA_X_MAX_DIST = 16384
+
+
 def attn_prefill_x(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache: torch.Tensor,
                    block_tables: torch.Tensor, bt_stride: int, cu_q_lens: torch.Tensor, context_lens: torch.Tensor,
                    tile_seq: torch.Tensor, tile_q0: torch.Tensor, num_tiles: int, out: torch.Tensor, nh: int, nkv: int,
@@ -721,10 +725,12 @@ def attn_prefill_x(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache:
     """Causal attention of prompt portions with keys of size d, values of size dv, ``v_share`` key
     heads to a value head, optional window and capped scores; out [T, nh*dv] in the cache's type or
     float32.  ``tile_*`` list tiles of 16 queries (general kernel, float32 arithmetic), ``tile64_*``
-    of 64 (mma.sync kernel: bfloat16, d and dv 64 or 128).  General kernel only: ``keep_first`` keys at
+    of 64 (mma.sync kernel: bfloat16, d and dv 64 or 128).  ``keep_first`` keys at
     the start of the sequence stay visible behind the window; ``dist_bias`` [rows, nh] float32 adds
     row dist_bucket[min(i - j, len(dist_bucket) - 1)] to the scaled score of query i and key j;
-    ``sigmoid_weights``: a visible key weighs sigmoid(score + head_bias[h]) and nothing is normalised."""
+    ``sigmoid_weights``: a visible key weighs sigmoid(score + head_bias[h]) and nothing is normalised.
+    With softmax these three are the general kernel's alone; with sigmoid weights the mma.sync kernel
+    has them too while dist_bucket has fewer than ATTN_MMA_X_MAX_DIST entries."""
     _attn_extras(nh, head_bias, dist_bias, dist_bucket)
     _check(lib().gg_attn_prefill_x(_p(q), ctypes.c_longlong(q_stride), _p(kcache), _p(vcache), dtype_code(kcache.dtype),
                                    _p(block_tables), bt_stride, _p(cu_q_lens), _p(context_lens), _p(tile_seq),

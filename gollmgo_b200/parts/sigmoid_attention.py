@@ -29,7 +29,7 @@ import torch
 from ..cache import PagedKVNeed
 from ..csrc import ops
 from ..weights import WeightSpec
-from .attention import TILES_GENERAL, Attention
+from .attention import ATTN_POLICY, TILES_GENERAL, TILES_MMA_X, Attention
 from .linear import linear
 from .registry import register_mixer
 
@@ -62,7 +62,10 @@ class SigmoidAttention(Attention):
         self.keep_first = int(spec.get("keep_first") or 0) if self.window else 0
         self.bias_max = int(spec["bias_max"])
         self.bias_rows = int(spec.get("bias_rows") or 32)
-        self._mma_x = False
+        # bfloat16 with heads of 64 or 128 and a distance table that fits in shared memory: mma.sync kernels
+        self._mma_x = (ctx.act_dtype == torch.bfloat16 and self.d in (64, 128) and ATTN_POLICY != "general"
+                       and self.bias_max < ops.ATTN_MMA_X_MAX_DIST
+                       and ctx.page_size & (ctx.page_size - 1) == 0)
         # the projection's columns: queries, keys (which are the values), then the output gate
         self.gate_col = (self.nh + self.nkv) * self.d
         self.qkv_width = -(-(self.gate_col + self.nh * self.d) // 8) * 8
@@ -75,7 +78,7 @@ class SigmoidAttention(Attention):
         return PagedKVNeed(self.nkv, self.d, self.window, shared_kv=True, keep_first=self.keep_first)
 
     def query_tiles(self):
-        return [TILES_GENERAL]
+        return [TILES_GENERAL, TILES_MMA_X] if self._mma_x else [TILES_GENERAL]
 
     def weights(self):
         n = self.tensor_names
@@ -120,10 +123,12 @@ class SigmoidAttention(Attention):
             if TILES_GENERAL not in batch.tiles:
                 raise RuntimeError("the step's batch was built without the index lists this mixer declares in "
                                    "query_tiles(): give them to the BatchBuilder (query_tiles=...)")
-            t16 = batch.tiles[TILES_GENERAL]
+            t16, t64 = batch.tiles[TILES_GENERAL], batch.tiles.get(TILES_MMA_X) if self._mma_x else None
             ops.attn_prefill_x(proj, self.qkv_width, kc, vc, bt, batch.bt_stride, batch.cu_q_lens, batch.context_lens,
                                t16.seq, t16.q0, t16.count, out, self.nh, self.nkv, self.d, self.d, 1,
-                               self.ctx.page_size, window, self.scale, 0.0, allow_mma=False, **extras)
+                               self.ctx.page_size, window, self.scale, 0.0,
+                               t64.seq if t64 else None, t64.q0 if t64 else None, t64.count if t64 else 0,
+                               allow_mma=t64 is not None, **extras)
         if batch.num_decode:
             n = batch.num_decode
             facts = getattr(batch, "facts", None)
@@ -132,7 +137,7 @@ class SigmoidAttention(Attention):
             ops.attn_decode_x(proj, self.qkv_width, kc, vc, bt, batch.bt_stride, batch.cu_q_lens, batch.context_lens,
                               batch.dec_seqs, n, splits, ws.get("attn_part_o", 1, n * self.nh * splits * self.d),
                               ws.get("attn_part_ml", 1, n * self.nh * splits * 2), out, self.nh, self.nkv, self.d,
-                              self.d, 1, self.ctx.page_size, window, self.scale, 0.0, allow_mma=False, **extras)
+                              self.d, 1, self.ctx.page_size, window, self.scale, 0.0, allow_mma=self._mma_x, **extras)
         gated = ws.get("attn_out", T, self.nh * self.d)
         ops.sigmoid_gate(out, proj[:, self.gate_col:self.gate_col + self.nh * self.d], gated)
         return linear(gated, self.w_o, ws.get(self.out_buffer, T, self.hidden), then)

@@ -288,7 +288,9 @@ def sigmoid_case(shape, n=420):
 # width, heads, kv heads, head size, window, kept first tokens, rows of the distance table, bias_max, page
 SIG_SHAPES = [(96, 4, 2, 32, 40, 3, 12, 60, 16), (128, 6, 1, 24, 24, 1, 20, 100, 8), (160, 4, 4, 128, 200, 4, 64, 300, 32),
               (104, 3, 3, 20, 5, 0, 8, 33, 8), (128, 4, 1, 64, None, 0, 40, 250, 16), (100, 6, 2, 12, 32, 11, 16, 90, 8),
-              (96, 2, 2, 40, 64, 2, 9, 500, 16)]
+              (96, 2, 2, 40, 64, 2, 9, 500, 16),
+              # heads of 64 in groups of four; more kept first tokens than one tile of keys holds
+              (128, 8, 2, 64, 70, 5, 16, 120, 16), (128, 4, 2, 64, 48, 70, 16, 120, 16)]
 
 
 def sigmoid_mixer(kit, dtype, D, m, rows, page, max_tokens=640):
