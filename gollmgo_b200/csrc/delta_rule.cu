@@ -117,7 +117,7 @@ __global__ void delta_conv_state_kernel(const TA* __restrict__ x, long long x_st
 
 // ---------------------------------------------------------------- the recurrence
 #define DR_COLS 16          // value columns of one CTA
-#define DR_LANES 8          // lanes that share a column: lane r holds rows r, r + 8, r + 16, ... of it
+#define DR_LANES 8          // lanes that share a column and split its d rows (dr_row)
 #define DR_CHUNK 16         // tokens staged in shared memory at a time
 #define DR_STAGE_FLOATS(dp) (2 * DR_CHUNK * (dp) + DR_CHUNK * DR_COLS + 2 * DR_CHUNK)
 // with a decay per key channel a stage also holds the decays [CHUNK][dp]
@@ -130,6 +130,26 @@ __device__ __forceinline__ void dr_cp4(float* dst, const float* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
 }
 
+// Which row of its column lane r holds in register i: four neighbouring rows at a time where there are
+// that many (one 16-byte read of shared memory brings a lane four rows of k, q or the decays, and the
+// lanes of a column together read 128 neighbouring bytes), else rows r, r + 8.
+template <int DPT> __device__ __forceinline__ int dr_row(int i, int r) {
+  return DPT >= 4 ? ((i >> 2) * (4 * DR_LANES) + r * 4 + (i & 3)) : (i * DR_LANES + r);
+}
+// lane r's DPT rows of one token's staged vector [dp]
+template <int DPT> __device__ __forceinline__ void dr_rows(float* dst, const float* src, int r) {
+  if constexpr (DPT >= 4) {
+#pragma unroll
+    for (int j = 0; j < DPT / 4; ++j) {
+      const float4 v = *reinterpret_cast<const float4*>(src + j * (4 * DR_LANES) + r * 4);
+      dst[4 * j] = v.x; dst[4 * j + 1] = v.y; dst[4 * j + 2] = v.z; dst[4 * j + 3] = v.w;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < DPT; ++i) dst[i] = src[i * DR_LANES + r];
+  }
+}
+
 // grid (B, H, ceil(dv / 16)), 128 threads.  state [slots, H, dv, d].  CH: decay is [T, H, d], one
 // factor per row of S (key channel), and acts before the token's read and write: S <- diag(g) S.
 // DELTA = false: the plain linear recurrence S <- g S + k (beta v)^T; o = S^T q (a state-space layer:
@@ -139,7 +159,7 @@ __global__ void __launch_bounds__(DR_COLS * DR_LANES)
 delta_recur_kernel(const float* __restrict__ qkv, const float* __restrict__ beta, const float* __restrict__ decay,
                    float* __restrict__ state, const int* __restrict__ cu_q_lens, const int* __restrict__ context_lens,
                    const int* __restrict__ state_slots, int G, int H, int d, int dv, float* __restrict__ o_raw) {
-  extern __shared__ float sm[];
+  extern __shared__ __align__(16) float sm[];
   pdl_trigger();
   const int b = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * DR_COLS;
   const int tid = threadIdx.x, r = tid & (DR_LANES - 1), cl = tid / DR_LANES, col = col0 + cl;
@@ -151,13 +171,13 @@ delta_recur_kernel(const float* __restrict__ qkv, const float* __restrict__ beta
   const int kvh = h / (H / G);
   const int dp = DPT * DR_LANES;                 // d rounded up to what the lanes hold
   float* ks = sm;                                // two stages of k [CHUNK][dp], q [CHUNK][dp], v [CHUNK][COLS], (beta, decay) [CHUNK][2]
-  float* os = sm + 2 * DR_STAGE_FLOATS_X(dp, CH);      // [CHUNK][COLS]
+  float* os = sm + 2 * DR_STAGE_FLOATS_X(dp, CH);      // [CHUNK][COLS][LANES]: every lane's share of o, summed after the chunk
   const bool live = col < dv;
   float S[DPT];
   float* srow = state + (((size_t)slot * H + h) * dv + (live ? col : 0)) * d;
 #pragma unroll
   for (int i = 0; i < DPT; ++i) {
-    const int row = i * DR_LANES + r;
+    const int row = dr_row<DPT>(i, r);
     S[i] = (live && start > 0 && row < d) ? srow[row] : 0.f;
   }
   pdl_wait();
@@ -231,19 +251,43 @@ delta_recur_kernel(const float* __restrict__ qkv, const float* __restrict__ beta
     const float* vcur = qc + DR_CHUNK * dp;
     const float* bg = vcur + DR_CHUNK * DR_COLS;
     const float* gc = bg + 2 * DR_CHUNK;
+    // The next token's k, q and decays are read into registers while this token is worked on: the
+    // reads of shared memory (which the compiler will not move above the store of the token before)
+    // then cost no time on the chain from one token's S to the next.  The sums run in four chains
+    // so that the additions overlap.
+    constexpr bool PRE = DPT <= 16;                // beyond that the registers would not hold two tokens
+    float kn[DPT], qn[DPT], gn[CH ? DPT : 1], ben = 0.f, gdn = 1.f;
+    if (PRE) {
+      dr_rows<DPT>(kn, kc, r);
+      dr_rows<DPT>(qn, qc, r);
+      if constexpr (CH) dr_rows<DPT>(gn, gc, r);
+      ben = bg[0];
+      if (!CH) gdn = bg[1];
+    }
 #pragma unroll 2
     for (int tt = 0; tt < n; ++tt) {
-      // lane r reads rows r, r + 8, ...: neighbouring lanes read neighbouring words (no bank
-      // conflicts), and the sums run in four chains so that the additions overlap
-      const float* kr = kc + tt * dp + r;
-      const float* qr = qc + tt * dp + r;
-      const float be = bg[tt * 2], g = CH ? 1.f : bg[tt * 2 + 1];
-      float kv[DPT];
+      float kv[DPT], qv[DPT], gv[CH ? DPT : 1], be, g = 1.f;
+      if (PRE) {
+#pragma unroll
+        for (int i = 0; i < DPT; ++i) { kv[i] = kn[i]; qv[i] = qn[i]; if constexpr (CH) gv[i] = gn[i]; }
+        be = ben; g = gdn;
+        const int nx = min(tt + 1, n - 1);
+        dr_rows<DPT>(kn, kc + nx * dp, r);
+        dr_rows<DPT>(qn, qc + nx * dp, r);
+        if constexpr (CH) dr_rows<DPT>(gn, gc + nx * dp, r);
+        ben = bg[nx * 2];
+        if (!CH) gdn = bg[nx * 2 + 1];
+      } else {
+        dr_rows<DPT>(kv, kc + tt * dp, r);
+        dr_rows<DPT>(qv, qc + tt * dp, r);
+        if constexpr (CH) dr_rows<DPT>(gv, gc + tt * dp, r);
+        be = bg[tt * 2];
+        if (!CH) g = bg[tt * 2 + 1];
+      }
       float d4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int i = 0; i < DPT; ++i) {
-        kv[i] = kr[i * DR_LANES];
-        if (CH) S[i] *= gc[tt * dp + r + i * DR_LANES];          // every row by its own factor, first
+        if constexpr (CH) S[i] *= gv[i];                         // every row by its own factor, first
         if (DELTA) d4[i & 3] = fmaf(kv[i], S[i], d4[i & 3]);
       }
       float dot = 0.f;
@@ -258,25 +302,25 @@ delta_recur_kernel(const float* __restrict__ qkv, const float* __restrict__ beta
 #pragma unroll
       for (int i = 0; i < DPT; ++i) {
         S[i] = fmaf(kv[i], u, g * S[i]);
-        o4[i & 3] = fmaf(qr[i * DR_LANES], S[i], o4[i & 3]);
+        o4[i & 3] = fmaf(qv[i], S[i], o4[i & 3]);
       }
-      float o = (o4[0] + o4[1]) + (o4[2] + o4[3]);
-      o += __shfl_xor_sync(0xffffffffu, o, 1);
-      o += __shfl_xor_sync(0xffffffffu, o, 2);
-      o += __shfl_xor_sync(0xffffffffu, o, 4);
-      if (r == 0) os[tt * DR_COLS + cl] = o;
+      // the lanes' shares of o are not needed by the next token: they go to shared memory as they are
+      // (a store the warp does not wait for), and are summed once the chunk is through
+      os[tt * (DR_COLS * DR_LANES) + tid] = (o4[0] + o4[1]) + (o4[2] + o4[3]);
     }
     __syncthreads();
     for (int e = tid; e < n * DR_COLS; e += blockDim.x) {
       const int tt = e / DR_COLS, cc = e - tt * DR_COLS;
-      if (col0 + cc < dv) o_raw[(size_t)(t0 + c0 + tt) * H * dv + (size_t)h * dv + col0 + cc] = os[e];
+      const float4 a = *reinterpret_cast<const float4*>(os + e * DR_LANES), c = *reinterpret_cast<const float4*>(os + e * DR_LANES + 4);
+      if (col0 + cc < dv)
+        o_raw[(size_t)(t0 + c0 + tt) * H * dv + (size_t)h * dv + col0 + cc] = ((a.x + a.y) + (a.z + a.w)) + ((c.x + c.y) + (c.z + c.w));
     }
   }
   asm volatile("cp.async.wait_group 0;" ::: "memory");
   if (live) {
 #pragma unroll
     for (int i = 0; i < DPT; ++i) {
-      const int row = i * DR_LANES + r;
+      const int row = dr_row<DPT>(i, r);
       if (row < d) srow[row] = S[i];
     }
   }
@@ -350,7 +394,7 @@ static int delta_recur_launch(const float* qkv, const float* beta, const float* 
                               const int* cu_q_lens, const int* context_lens, const int* state_slots, int B, int G, int H,
                               int d, int dv, float* o_raw, cudaStream_t stream) {
   const int dp = DPT * DR_LANES;
-  const size_t smem = (size_t)(2 * DR_STAGE_FLOATS_X(dp, CH) + DR_CHUNK * DR_COLS) * sizeof(float);
+  const size_t smem = (size_t)(2 * DR_STAGE_FLOATS_X(dp, CH) + DR_CHUNK * DR_COLS * DR_LANES) * sizeof(float);
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(delta_recur_kernel<DPT, CH, DELTA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return gg_fail(GG_ERR_CUDA, "delta_recur: %s", cudaGetErrorString(e));
