@@ -55,6 +55,21 @@ inline cudaError_t gg_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, si
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// The same without the attribute: the kernel starts when everything ahead of it in the stream has
+// completed.  For a kernel of few long-running blocks, whose blocks should find an empty machine:
+// launched early they are placed where the predecessor leaves room first, several on one
+// multiprocessor and none on others, and stay there.
+template <typename... KArgs, typename... Args>
+inline cudaError_t gg_launch_after(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                   cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 __device__ __forceinline__ float to_f32(float x) { return x; }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 x) { return __bfloat162float(x); }
 template <typename T> __device__ __forceinline__ T from_f32(float x);

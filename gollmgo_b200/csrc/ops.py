@@ -876,7 +876,8 @@ def delta_recur(qkv: torch.Tensor, beta: torch.Tensor, decay: torch.Tensor, stat
         raise KernelError("delta_recur: state must be float32 [slots, heads, dv, d]")
     dw = decay.shape[-1] // heads
     _check(lib().gg_delta_recur(_p(qkv), _p(beta), _p(decay), _p(state), _p(cu_q_lens), _p(context_lens),
-                                _p(state_slots), num_seqs, kv_heads, heads, d, dv, dw, int(plain), _p(o_raw), _stream()))
+                                _p(state_slots), num_seqs, kv_heads, heads, d, dv, dw, int(plain), o_raw.shape[0], _p(o_raw),
+                                _stream()))
 
 
 def delta_out(o_raw: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, heads: int, dv: int,

@@ -103,7 +103,9 @@ TWO = [{"a": (0, 9), "b": (0, 2)}, {"a": (9, 10)}, {"b": (2, 19), "a": (10, 11)}
 
 # width, heads, values, state, groups, taps, norm parts
 SSM_SHAPES = [(64, 4, 16, 24, 2, 4, 2), (96, 8, 16, 32, 4, 3, 4), (100, 5, 12, 20, 5, 5, 1), (72, 3, 20, 8, 1, 1, 3),
-              (128, 2, 64, 128, 1, 4, 1), (80, 2, 24, 200, 2, 2, 2)]
+              (128, 2, 64, 128, 1, 4, 1), (80, 2, 24, 200, 2, 2, 2),
+              # values in multiples of 32 a head (a thread of the recurrence then holds two columns) with small and odd states
+              (64, 3, 32, 16, 1, 3, 1), (96, 2, 96, 48, 2, 4, 2)]
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
