@@ -1268,32 +1268,45 @@ __global__ void __launch_bounds__(MMA_THREADS) attn_decode_mma_x_kernel(AttnArgs
           load_tile_of<DV>(vc, nv, vh, bt, tile_kb(it + 1), tile_lo(it + 1), tile_hi(it + 1), base + st * STAGE + K_BYTES, ps_log2);
       }
       cp_async_commit();
+      const int key0 = warp * 16;
+      const int tok0 = tile_kb(it) + key0, thi = tile_hi(it);
+      // SIG: the biases of this thread's scores (rows g and g + 8 of the tile are heads head0 + g and
+      // head0 + g + 8, clamped where the group is smaller), read while the tile is still on its way
+      float bias0[2][2], bias1[2][2];
+      if (SIG) {
+        const int hr0 = head0 + min(g, nrows - 1), hr1 = head0 + min(g + 8, nrows - 1);
+        const float hb0 = a.head_bias ? a.head_bias[hr0] : 0.f, hb1 = a.head_bias ? a.head_bias[hr1] : 0.f;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int tk = tok0 + j * 8 + c2 + e;
+            bias0[j][e] = hb0;
+            bias1[j][e] = hb1;
+            if (tk < thi && a.dist_bias) {
+              const size_t row = (size_t)a.dist_bucket[min(ctx - 1 - tk, a.dist_max)] * a.nh;
+              bias0[j][e] += a.dist_bias[row + hr0];
+              bias1[j][e] += a.dist_bias[row + hr1];
+            }
+          }
+        }
+      }
       cp_async_wait<STAGES - 1>();
       __syncthreads();
       const int st = it % STAGES;
       const unsigned ks = base + st * STAGE, vs = kv_same ? ks : ks + K_BYTES;
-      const int key0 = warp * 16;
-      const int tok0 = tile_kb(it) + key0, thi = tile_hi(it);
       if (tok0 < thi) {
         float s[2][4];
         qk_mma<DK, 2>(qf, ks, key0, s);
         unsigned p[1][4];
         if (SIG) {
-          // rows g and g + 8 of the tile are heads head0 + g and head0 + g + 8 (clamped where the group is smaller)
-          const int hr0 = head0 + min(g, nrows - 1), hr1 = head0 + min(g + 8, nrows - 1);
-          const float hb0 = a.head_bias ? a.head_bias[hr0] : 0.f, hb1 = a.head_bias ? a.head_bias[hr1] : 0.f;
 #pragma unroll
           for (int j = 0; j < 2; ++j) {
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
               const int tk = tok0 + j * 8 + c2 + e;
               const bool ok = tk < thi;
-              float b0 = hb0, b1 = hb1;
-              if (ok && a.dist_bias) {
-                const size_t row = (size_t)a.dist_bucket[min(ctx - 1 - tk, a.dist_max)] * a.nh;
-                b0 += a.dist_bias[row + hr0];
-                b1 += a.dist_bias[row + hr1];
-              }
+              const float b0 = bias0[j][e], b1 = bias1[j][e];
               float x0 = s[j][e] * scale, x1 = s[j][2 + e] * scale;
               if (cap > 0.f) {
                 float th;

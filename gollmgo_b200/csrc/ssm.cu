@@ -131,7 +131,9 @@ extern "C" int gg_ssm_out(const float* y_raw, const float* cbx, int x_col, int C
   const int inner = H * P, part = inner / parts;
   const size_t smem = (size_t)(part + 33) * sizeof(float);
   GG_REQUIRE(smem <= 200 * 1024, "ssm_out: parts of %d values do not fit in shared memory", part);
-  const int threads = part >= 1024 ? 256 : (part >= 256 ? 128 : 64);
+  // four values a thread where the part is long: a step of few decoded tokens has T * parts blocks and waits on
+  // each thread's chain of reads
+  const int threads = part >= 4096 ? 1024 : (part >= 2048 ? 512 : (part >= 1024 ? 256 : (part >= 256 ? 128 : 64)));
   const dim3 grid(T, parts);
   cudaError_t e = cudaSuccess;
   if (dtype == GG_F32) {

@@ -70,10 +70,10 @@ FAP_C = {"architecture": "Fapudra", "vocab": 150, "width": 100, "norm": {"eps": 
              _layer(_ssm(3, 20, 8, 1, 3, 3), _moe(52, 2.5, 3, 3)),
          ]}
 # the widest kernels: heads of 128, states of 128 x 128, a window longer than most requests
-FAP_D = {"architecture": "Fapudra", "vocab": 512, "width": 256, "norm": {"eps": 1e-6}, "embedding": {"scale": 16.0},
+FAP_D = {"architecture": "Fapudra", "vocab": 384, "width": 256, "norm": {"eps": 1e-6}, "embedding": {"scale": 16.0},
          "max_positions": 1024, "logit_softcap": 20.0, "layers": [
              _layer(_ssm(4, 64, 128, 1, 4, 1), _moe(128, 1.0, 8, 2, 2, 1)),
-             _layer(_par(_left(4, 2, 128, 0.09, 300, 64, window=200, first=4), _right(2, 1, 128, 128, 4, 32, 32), 0.8, 0.5),
+             _layer(_par(_left(4, 2, 128, 0.09, 300, 64, window=200, first=6), _right(2, 1, 128, 128, 4, 32, 32), 0.75, 0.55),
                     _moe(96, 1.0, 16, 4, 4, 2)),
          ]}
 
