@@ -77,8 +77,18 @@ FAP_D = {"architecture": "Fapudra", "vocab": 384, "width": 256, "norm": {"eps": 
                     _moe(96, 1.0, 16, 4, 4, 2)),
          ]}
 
+# heads of 64 in groups of four with a window a little longer than a tile of keys and more kept tokens than a page;
+# states whose columns a thread holds two of; a state that fills no whole register block
+FAP_E = {"architecture": "Fapudra", "vocab": 300, "width": 192, "norm": {"eps": 2e-6}, "embedding": {"scale": 11.0},
+         "max_positions": 640, "logit_softcap": 25.0, "layers": [
+             _layer(_ssm(6, 32, 40, 2, 3, 2), _moe(80, 1.4, 6, 2, 2, 1)),
+             _layer(_par(_left(8, 2, 64, 0.12, 150, 24, window=72, first=19), _right(4, 2, 32, 64, 3, 12, 20), 0.6, 0.7),
+                    _moe(64, 2.0, 4, 2)),
+             _layer(_ssm(3, 64, 16, 3, 2, 1), None),
+         ]}
+
 # name -> (config, page size)
-TINY = {"fap_a": (FAP_A, 16), "fap_b": (FAP_B, 8), "fap_c": (FAP_C, 8), "fap_d": (FAP_D, 32)}
+TINY = {"fap_a": (FAP_A, 16), "fap_b": (FAP_B, 8), "fap_c": (FAP_C, 8), "fap_d": (FAP_D, 32), "fap_e": (FAP_E, 16)}
 
 
 def get(name):

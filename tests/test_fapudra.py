@@ -577,7 +577,7 @@ def test_parallel_mixer_with_token_shift(kit, dtype, name):
 # ------------------------------------------------------------------ whole models through bin/trace_run
 # longer than every window plus what is decoded one by one; one request of a single token and short ones
 LENGTHS = {"fap_a": [1, 5, 37, 70, 130, 96], "fap_b": [2, 64, 65, 131, 90, 33], "fap_c": [3, 66, 40, 150, 97, 129],
-           "fap_d": [4, 17, 290, 33, 65, 120]}
+           "fap_d": [4, 17, 290, 33, 65, 120], "fap_e": [2, 73, 160, 31, 210, 95]}
 # float32: every row to a few units of rounding.  bfloat16: nine rows in ten within 4 % of the row's largest
 # logit and none further off than what a lost key or state would cause (such a row is off by its whole size).
 TOL = {"float32": (5e-5, 5e-5), "bfloat16": (4e-2, 0.15)}
