@@ -88,7 +88,8 @@ __device__ __forceinline__ void attn_tile(const AttnArgs& a, int nrows, const TA
       for (int i = 0; i < 8; ++i) {
         const int r = rb + 2 * i;
         const int p = pos_s[r];
-        const bool ok = tok >= lo && tok < hi && tok <= p && (a.window <= 0 || tok > p - a.window || tok < a.keep_first);
+        const bool ok = tok >= lo && tok < hi && tok <= p && (a.window <= 0 || tok > p - a.window || tok < a.keep_first) &&
+                        (a.chunk <= 0 || tok >= (p / a.chunk) * a.chunk);
         float sc = s[i] * a.scale;
         if (a.softcap > 0.f) sc = a.softcap * tanhf(sc / a.softcap);
         if (ok && a.dist_bias) sc += a.dist_bias[(size_t)a.dist_bucket[min(p - tok, a.dist_max)] * a.nh + head_s[r]];
@@ -174,12 +175,30 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_prefill_kernel(AttnArgs a) {
   }
   __syncthreads();
   const int first = qstart + q0, last = first + nrows - 1;
-  const int lo = a.window > 0 ? max(0, first - a.window + 1) : 0;
+  int lo = a.window > 0 ? max(0, first - a.window + 1) : 0;
+  if (a.chunk > 0) lo = max(lo, (first / a.chunk) * a.chunk);       // the chunk of the tile's first row starts earliest
   float acc[NACC];
   attn_tile<TA, DMAX>(a, nrows, qptr_s, pos_s, head_s, kvh, a.block_tables + (size_t)b * a.bt_stride, lo, last + 1,
                       min(a.keep_first, lo), smem, acc);
   pdl_trigger();
-  const float* l_s = attn_tile_max(a, smem) + ATT_BQ;
+  float* m_s = const_cast<float*>(attn_tile_max(a, smem));
+  float* l_s = m_s + ATT_BQ;
+  if (a.sink) {                                  // one more term of the denominator: rows rescaled to max(m, sink)
+    __shared__ float sink_f[ATT_BQ];
+    if (threadIdx.x < ATT_BQ) {
+      const int r = threadIdx.x;
+      const float sk = a.sink[h], m = m_s[r], M = fmaxf(m, sk);
+      const float f = m == -INFINITY ? 0.f : expf(m - M);
+      sink_f[r] = f;
+      l_s[r] = l_s[r] * f + expf(sk - M);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < NACC; ++i) {
+      const int e = threadIdx.x + ATT_THREADS * i;
+      if (e < ATT_BQ * (a.dv > 0 ? a.dv : a.d)) acc[i] *= sink_f[e / (a.dv > 0 ? a.dv : a.d)];
+    }
+  }
   const int dv = a.dv > 0 ? a.dv : a.d;
 #pragma unroll
   for (int i = 0; i < NACC; ++i) {
@@ -214,7 +233,8 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(AttnArgs a) {
   const int nrows = min(ATT_BQ, G - g0);
   const int ctx = b >= 0 ? a.context_lens[b] : 0;      // b < 0: padding of a captured batch
   const int t = b >= 0 ? a.cu_q_lens[b] : 0;
-  const int lo0 = a.window > 0 ? max(0, ctx - a.window) : 0;
+  int lo0 = a.window > 0 ? max(0, ctx - a.window) : 0;
+  if (a.chunk > 0 && ctx > 0) lo0 = max(lo0, ((ctx - 1) / a.chunk) * a.chunk);
   const int n = ctx - lo0;
   int chunk = (n + S - 1) / S;
   chunk = ((chunk + ATT_BK - 1) / ATT_BK) * ATT_BK;
@@ -269,7 +289,8 @@ __global__ void attn_merge_kernel(AttnArgs a) {
   const size_t row0 = ((size_t)blockIdx.x * a.nh + h) * S;
   float M = -INFINITY;
   for (int s = 0; s < S; ++s) M = fmaxf(M, a.part_ml[(row0 + s) * 2]);
-  float L = 0.f;
+  if (a.sink) M = fmaxf(M, a.sink[h]);
+  float L = a.sink ? expf(a.sink[h] - M) : 0.f;
   for (int s = 0; s < S; ++s) {
     const float m = a.part_ml[(row0 + s) * 2];
     if (m != -INFINITY) L += expf(m - M) * a.part_ml[(row0 + s) * 2 + 1];
@@ -507,6 +528,8 @@ extern "C" int gg_attn_decode_cluster_capacity(int dtype, int d, int splits, int
   return attn_decode_cluster_capacity(d, splits, group);
 }
 
+extern "C" int gg_attn_mma_x_chunk_sink() { return attn_mma_x_chunk_sink_supported() ? 1 : 0; }
+
 // The general kernels with everything they take: keys of size d and values of size dv, `v_share`
 // consecutive key heads reading one value head (vcache [num_pages, nkv / v_share, page_size, dv]),
 // scores capped by softcap * tanh(score / softcap) where softcap > 0, the result in float32 where
@@ -517,7 +540,7 @@ extern "C" int gg_attn_prefill_x(const void* q, long long q_stride, const void* 
                                  const int* tile64_seq, const int* tile64_q0, int num_tiles64, int allow_mma,
                                  void* out, int out_f32, int nh, int nkv, int d, int dv, int v_share,
                                  int page_size, int window, float scale, float softcap, int keep_first, int weights,
-                                 const float* head_bias, const float* dist_bias, const int* dist_bucket, int dist_max,
+                                 const float* head_bias, const float* dist_bias, const int* dist_bucket, int dist_max, int chunk, const float* sink,
                                  cudaStream_t stream) {
   AttnArgs a = {};
   a.q = q; a.q_stride = q_stride; a.kcache = kcache; a.vcache = vcache;
@@ -528,12 +551,15 @@ extern "C" int gg_attn_prefill_x(const void* q, long long q_stride, const void* 
   a.tile_seq = tile_seq; a.tile_q0 = tile_q0;
   a.keep_first = window > 0 ? keep_first : 0; a.weights = weights; a.head_bias = head_bias;
   a.dist_bias = dist_bias; a.dist_bucket = dist_bucket; a.dist_max = dist_max;
+  a.chunk = chunk > 0 ? chunk : 0; a.sink = sink;
   int rc = check_common(a, "attn_prefill_x");
   if (rc) return rc;
   GG_REQUIRE(weights == 0 || weights == 1, "attn_prefill_x: unknown kind of weights %d", weights);
   GG_REQUIRE(!dist_bias || (dist_bucket && dist_max >= 0), "attn_prefill_x: a distance bias needs its bucket table");
+  GG_REQUIRE(!(weights && (a.chunk || sink)), "attn_prefill_x: chunks and a sink go with softmax weights");
   // what the mma.sync kernels compute: softmax without these extras, or sigmoid weights with all of them
   const bool plain = (!a.keep_first && !weights && !head_bias && !dist_bias) || attn_mma_x_sigmoid_supported(a);
+  if (a.chunk || a.sink) allow_mma = allow_mma && attn_mma_x_chunk_sink_supported();
   // bfloat16 with sizes of 64 or 128: the mma.sync kernel over tiles of 64 queries
   if (plain && allow_mma && tile64_seq && attn_mma_x_supported(dtype, d, dv > 0 ? dv : d, page_size) && q_stride % 8 == 0) {
     a.tile_seq = tile64_seq; a.tile_q0 = tile64_q0;
@@ -548,7 +574,8 @@ extern "C" int gg_attn_decode_x(const void* q, long long q_stride, const void* k
                                 float* part_o, float* part_ml, void* out, int out_f32, int nh, int nkv, int d,
                                 int dv, int v_share, int page_size, int window, float scale, float softcap,
                                 int allow_mma, int keep_first, int weights, const float* head_bias,
-                                const float* dist_bias, const int* dist_bucket, int dist_max, cudaStream_t stream) {
+                                const float* dist_bias, const int* dist_bucket, int dist_max, int chunk, const float* sink,
+                                cudaStream_t stream) {
   AttnArgs a = {};
   a.q = q; a.q_stride = q_stride; a.kcache = kcache; a.vcache = vcache;
   a.block_tables = block_tables; a.bt_stride = bt_stride; a.cu_q_lens = cu_q_lens;
@@ -558,12 +585,15 @@ extern "C" int gg_attn_decode_x(const void* q, long long q_stride, const void* k
   a.dec_seqs = dec_seqs; a.num_splits = num_splits; a.part_o = part_o; a.part_ml = part_ml;
   a.keep_first = window > 0 ? keep_first : 0; a.weights = weights; a.head_bias = head_bias;
   a.dist_bias = dist_bias; a.dist_bucket = dist_bucket; a.dist_max = dist_max;
+  a.chunk = chunk > 0 ? chunk : 0; a.sink = sink;
   int rc = check_common(a, "attn_decode_x");
   if (rc) return rc;
   GG_REQUIRE(weights == 0 || weights == 1, "attn_decode_x: unknown kind of weights %d", weights);
   GG_REQUIRE(!dist_bias || (dist_bucket && dist_max >= 0), "attn_decode_x: a distance bias needs its bucket table");
+  GG_REQUIRE(!(weights && (a.chunk || sink)), "attn_decode_x: chunks and a sink go with softmax weights");
   if ((a.keep_first || weights || head_bias || dist_bias) && !attn_mma_x_sigmoid_supported(a))
     allow_mma = 0;                                                            // only the general kernel has these with softmax
+  if (a.chunk) allow_mma = allow_mma && attn_mma_x_chunk_sink_supported();     // (the sink is the merge kernel's)
   GG_REQUIRE(n_dec >= 0 && num_splits >= 1 && num_splits <= 65535, "attn_decode_x: bad n_dec %d or splits %d", n_dec, num_splits);
   GG_REQUIRE(part_o && part_ml, "attn_decode_x: no scratch given");
   if (n_dec == 0) return GG_OK;

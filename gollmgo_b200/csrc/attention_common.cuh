@@ -40,6 +40,9 @@ struct AttnArgs {
   const float* dist_bias;   // [rows, nh]: row dist_bucket[min(i - j, dist_max)] is added to the scaled score; null = none
   const int* dist_bucket;   // [dist_max + 1]
   int dist_max;
+  int chunk;                // > 0: the sequence is cut into chunks of this many positions, counted from 0, and a query sees
+                            // only the keys of its own chunk (all kernels but the tcgen05 ones and the plain mma.sync ones)
+  const float* sink;        // [nh] or null: exp(sink[h]) is one more term of the softmax denominator, with no key and no value
 };
 
 // General kernels (attention.cu)
@@ -58,6 +61,8 @@ int attn_prefill_mma_x(const AttnArgs& a, int num_tiles, cudaStream_t stream);  
 // a.weights == 1 (sigmoid weights, kept first keys, biases by head and distance) on the same kernels
 #define ATTN_MMA_X_MAX_DIST 16384      // entries of the distance table that fit in shared memory beside the tiles
 bool attn_mma_x_sigmoid_supported(const AttnArgs& a);
+// a.chunk and a.sink with softmax weights on the same kernels
+bool attn_mma_x_chunk_sink_supported();
 int attn_decode_mma_x(const AttnArgs& a, int n_dec, cudaStream_t stream);        // partial results; the caller merges
 // large batches: the tiles of all (token, kv head) pairs cut into equal ranges, one per CTA
 int attn_decode_flat_ctas(int d);

@@ -1398,6 +1398,8 @@ static int prefill_x_go(const AttnArgs& a, int num_tiles, cudaStream_t stream) {
 
 // what the SIG kernels take: sigmoid weights (with or without the biases and kept first keys), and a
 // table over distances that fits beside the staged tiles
+bool attn_mma_x_chunk_sink_supported() { return false; }
+
 bool attn_mma_x_sigmoid_supported(const AttnArgs& a) {
   return a.weights == 1 && a.dist_max >= 0 && a.dist_max < ATTN_MMA_X_MAX_DIST && (!a.dist_bias || a.dist_bucket);
 }

@@ -51,6 +51,75 @@ extern "C" int gg_latent_norm_write(const void* src, long long src_stride, int c
   return gg_check_launch("latent_norm_write");
 }
 
+// The rotated part of a latent attention whose keys have, beside what is expanded from the latent, `rot`
+// values that carry the position and are shared by all heads.  For token t: the key part (columns
+// [k_col0, k_col0 + rot) of the projection row) is rotated and written to columns [dst_col, dst_col + rot)
+// of the cache row at slot[t] (rows of `row` values; the latent occupies the columns before), and every
+// head's query part (columns [h * q_head + q_off, + rot) of the row) is rotated and written to columns
+// [h * row + dst_col, + rot) of qout[t].  Pairs (2i, 2i+1) if interleaved, else (i, i + rot/2); cosines
+// and sines times mag; the angle is reduced in float64.
+template <typename TA>
+__global__ void latent_rope_kernel(const TA* __restrict__ src, long long src_stride, int k_col0, int q_head, int q_off,
+                                   int H, int rot, const int* __restrict__ positions, const double* __restrict__ inv_freq,
+                                   float mag, int interleaved, const int* __restrict__ slots, TA* __restrict__ cache,
+                                   TA* __restrict__ qout, long long q_stride, int row, int dst_col, int write_cache) {
+  extern __shared__ float cs[];        // cos[rot/2], sin[rot/2]
+  pdl_trigger();
+  const int t = blockIdx.x, half = rot >> 1;
+  {
+    const double pos = (double)positions[t];
+    const double two_pi = 6.283185307179586476925286766559;
+    for (int p = threadIdx.x; p < half; p += blockDim.x) {
+      const double ang = pos * inv_freq[p];
+      const float r = (float)(ang - two_pi * rint(ang * (1.0 / two_pi)));
+      float s, c;
+      sincosf(r, &s, &c);
+      cs[p] = c * mag;
+      cs[half + p] = s * mag;
+    }
+  }
+  const int slot = (write_cache && slots) ? slots[t] : -1;
+  __syncthreads();
+  pdl_wait();
+  const TA* x = src + (size_t)t * src_stride;
+  // unit 0: the key part; unit 1 + h: head h's query part
+  for (int e = threadIdx.x; e < (H + 1) * half; e += blockDim.x) {
+    const int unit = e / half, p = e - unit * half;
+    const int i0 = interleaved ? 2 * p : p, i1 = interleaved ? 2 * p + 1 : p + half;
+    const TA* in = unit == 0 ? x + k_col0 : x + (size_t)(unit - 1) * q_head + q_off;
+    TA* out = unit == 0 ? (slot >= 0 ? cache + (size_t)slot * row + dst_col : nullptr)
+                        : qout + (size_t)t * q_stride + (size_t)(unit - 1) * row + dst_col;
+    if (!out) continue;
+    const float u = to_f32(in[i0]), v = to_f32(in[i1]);
+    const float c = cs[p], s = cs[half + p];
+    out[i0] = from_f32<TA>(u * c - v * s);
+    out[i1] = from_f32<TA>(v * c + u * s);
+  }
+}
+
+extern "C" int gg_latent_rope(const void* src, long long src_stride, int k_col0, int q_head, int q_off, int H, int rot,
+                              const int* positions, const double* inv_freq, float mag, int interleaved, const int* slots,
+                              void* cache, void* qout, long long q_stride, int row, int dst_col, int write_cache,
+                              int act_dtype, int T, cudaStream_t stream) {
+  GG_REQUIRE(T >= 0 && H > 0 && rot > 0 && rot % 2 == 0 && dst_col >= 0 && dst_col + rot <= row,
+             "latent_rope: bad sizes T=%d H=%d rot=%d row=%d col=%d", T, H, rot, row, dst_col);
+  GG_REQUIRE(src && positions && inv_freq && qout && q_stride >= (long long)H * row, "latent_rope: a pointer is null or the query rows are too short");
+  GG_REQUIRE(!write_cache || (cache && slots), "latent_rope: cache write without cache or slots");
+  if (T == 0) return GG_OK;
+  const size_t smem = (size_t)rot * sizeof(float);
+  GG_REQUIRE(smem <= 48 * 1024, "latent_rope: rotary width %d too large", rot);
+  if (act_dtype == GG_F32)
+    gg_launch(latent_rope_kernel<float>, dim3(T), dim3(128), smem, stream, (const float*)src, src_stride, k_col0, q_head, q_off, H,
+              rot, positions, inv_freq, mag, interleaved, slots, (float*)cache, (float*)qout, q_stride, row, dst_col, write_cache);
+  else if (act_dtype == GG_BF16)
+    gg_launch(latent_rope_kernel<__nv_bfloat16>, dim3(T), dim3(128), smem, stream, (const __nv_bfloat16*)src, src_stride, k_col0,
+              q_head, q_off, H, rot, positions, inv_freq, mag, interleaved, slots, (__nv_bfloat16*)cache, (__nv_bfloat16*)qout,
+              q_stride, row, dst_col, write_cache);
+  else
+    return gg_fail(GG_ERR_INVALID, "latent_rope: unknown dtype %d", act_dtype);
+  return gg_check_launch("latent_rope");
+}
+
 // a[t, h * n .. h * n + n) *= sigmoid(gates[t, col0 + h]): the output gate of an attention head, for
 // steps whose per-head products ran in the vendor library.
 template <typename TA>

@@ -215,3 +215,49 @@ extern "C" int gg_cast_rows(const float* resid, void* copy, int act_dtype, long 
     return gg_fail(GG_ERR_INVALID, "cast_rows: unknown dtype %d", act_dtype);
   return gg_check_launch("cast_rows");
 }
+
+
+// resid[t] += n(x[t]) with x = (y[t] + yb) * sigmoid(g[t] + gb), n the RMS norm with weight w: a block whose
+// sublayers' results pass a learned gate (g = a product of the sublayer's own input, gb its bias) and then a
+// norm before they join the residual stream.  yb: a bias of the sublayer's last product that was left to this
+// kernel (null: none); g null: no gate.  The gate, the statistics and the sum are float32.
+template <typename TA>
+__global__ void gate_norm_add_kernel(float* __restrict__ resid, const TA* __restrict__ y, const float* __restrict__ yb,
+                                     const TA* __restrict__ g, long long g_stride, const float* __restrict__ gb,
+                                     const float* __restrict__ w, int H, float eps) {
+  extern __shared__ __align__(16) float xs[];
+  float* red = xs + H;
+  pdl_trigger();
+  pdl_wait();
+  const size_t t = blockIdx.x;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < H; c += blockDim.x) {
+    float x = to_f32(y[t * H + c]) + (yb ? yb[c] : 0.f);
+    if (g) x /= 1.f + expf(-(to_f32(g[t * g_stride + c]) + (gb ? gb[c] : 0.f)));
+    xs[c] = x;
+    ss += x * x;
+  }
+  const float rinv = rsqrtf(block_sum(ss, red) / (float)H + eps);
+  float* xr = resid + t * H;
+  for (int c = threadIdx.x; c < H; c += blockDim.x) xr[c] += xs[c] * rinv * w[c];
+}
+
+extern "C" int gg_gate_norm_add(float* resid, const void* y, const float* yb, const void* g, long long g_stride,
+                                const float* gb, const float* w, int act_dtype, int T, int H, float eps, cudaStream_t stream) {
+  GG_REQUIRE(T >= 0 && H > 0 && eps >= 0.f, "gate_norm_add: bad sizes T=%d H=%d eps=%g", T, H, (double)eps);
+  GG_REQUIRE(resid && y && w && (!g || g_stride >= H), "gate_norm_add: residual, input and weight are needed");
+  if (T == 0) return GG_OK;
+  const size_t smem = (size_t)(H + 33) * sizeof(float);
+  GG_REQUIRE(smem <= 200 * 1024, "gate_norm_add: rows of %d values do not fit in shared memory", H);
+  const int threads = H >= 2048 ? 512 : 256;
+  if (act_dtype == GG_F32) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(gate_norm_add_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    gg_launch(gate_norm_add_kernel<float>, dim3(T), dim3(threads), smem, stream, resid, (const float*)y, yb, (const float*)g, g_stride, gb, w, H, eps);
+  } else if (act_dtype == GG_BF16) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(gate_norm_add_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    gg_launch(gate_norm_add_kernel<__nv_bfloat16>, dim3(T), dim3(threads), smem, stream, resid, (const __nv_bfloat16*)y, yb, (const __nv_bfloat16*)g, g_stride, gb, w, H, eps);
+  } else {
+    return gg_fail(GG_ERR_INVALID, "gate_norm_add: unknown dtype %d", act_dtype);
+  }
+  return gg_check_launch("gate_norm_add");
+}

@@ -371,3 +371,62 @@ extern "C" int gg_sigmoid_gate(const float* a, const void* g, long long g_stride
   else return gg_fail(GG_ERR_INVALID, "sigmoid_gate: unknown dtype %d", dtype);
   return gg_check_launch("sigmoid_gate");
 }
+
+
+// out[t, c] = act(gu[t, c] + bias[c]) * (gu[t, I + c] + bias[I + c]): the inner step of a gated feed-forward whose
+// two first products have biases (bias null: none).  kind 0: relu, 1: gelu (tanh form), 2: silu.
+__device__ __forceinline__ float gated_act_apply(float z, int kind) {
+  if (kind == 0) return fmaxf(z, 0.f);
+  if (kind == 1) return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+  return z / (1.f + expf(-z));
+}
+
+template <typename TA>
+__global__ void gated_act_kernel(const TA* __restrict__ gu, const float* __restrict__ bias, TA* __restrict__ out, int I, int kind) {
+  pdl_trigger();
+  pdl_wait();
+  const size_t t = blockIdx.y;
+  const TA* row = gu + t * 2 * I;
+  for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < I; c += gridDim.x * blockDim.x) {
+    const float g = to_f32(row[c]) + (bias ? bias[c] : 0.f), u = to_f32(row[I + c]) + (bias ? bias[I + c] : 0.f);
+    out[t * I + c] = from_f32<TA>(gated_act_apply(g, kind) * u);
+  }
+}
+
+extern "C" int gg_gated_act(const void* gu, const float* bias, void* out, int T, int I, int kind, int dtype, cudaStream_t stream) {
+  GG_REQUIRE(T >= 0 && I > 0 && gu && out && kind >= 0 && kind <= 2, "gated_act: bad arguments T=%d I=%d kind=%d", T, I, kind);
+  if (T == 0) return GG_OK;
+  int gx = (I + 255) / 256;
+  if (gx > 64) gx = 64;
+  for (int t0 = 0; t0 < T; t0 += 65535) {
+    const int n = T - t0 < 65535 ? T - t0 : 65535;
+    const dim3 grid(gx, n);
+    if (dtype == GG_F32) gg_launch(gated_act_kernel<float>, grid, dim3(256), 0, stream, (const float*)gu + (size_t)t0 * 2 * I, bias, (float*)out + (size_t)t0 * I, I, kind);
+    else if (dtype == GG_BF16) gg_launch(gated_act_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, (const __nv_bfloat16*)gu + (size_t)t0 * 2 * I, bias, (__nv_bfloat16*)out + (size_t)t0 * I, I, kind);
+    else return gg_fail(GG_ERR_INVALID, "gated_act: unknown dtype %d", dtype);
+  }
+  return gg_check_launch("gated_act");
+}
+
+// a[t, c] *= sigmoid(g[t, c]) in place; a rows of W values, g rows of stride g_stride, both of the activation type
+template <typename TA>
+__global__ void gate_mul_kernel(TA* __restrict__ a, const TA* __restrict__ g, long long g_stride, long long n, int W) {
+  pdl_trigger();
+  pdl_wait();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / W;
+    const float z = to_f32(g[t * g_stride + (i - t * W)]);
+    a[i] = from_f32<TA>(to_f32(a[i]) / (1.f + expf(-z)));
+  }
+}
+
+extern "C" int gg_gate_mul(void* a, const void* g, long long g_stride, int T, int W, int dtype, cudaStream_t stream) {
+  GG_REQUIRE(T >= 0 && W > 0 && a && g && g_stride >= W, "gate_mul: bad arguments T=%d W=%d", T, W);
+  if (T == 0) return GG_OK;
+  const long long n = (long long)T * W;
+  const int blocks = (int)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096);
+  if (dtype == GG_F32) gg_launch(gate_mul_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)a, (const float*)g, g_stride, n, W);
+  else if (dtype == GG_BF16) gg_launch(gate_mul_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (__nv_bfloat16*)a, (const __nv_bfloat16*)g, g_stride, n, W);
+  else return gg_fail(GG_ERR_INVALID, "gate_mul: unknown dtype %d", dtype);
+  return gg_check_launch("gate_mul");
+}

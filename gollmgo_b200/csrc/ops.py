@@ -721,7 +721,8 @@ def attn_prefill_x(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache:
                    tile64_seq: Optional[torch.Tensor] = None, tile64_q0: Optional[torch.Tensor] = None,
                    num_tiles64: int = 0, allow_mma: bool = True, keep_first: int = 0, sigmoid_weights: bool = False,
                    head_bias: Optional[torch.Tensor] = None, dist_bias: Optional[torch.Tensor] = None,
-                   dist_bucket: Optional[torch.Tensor] = None) -> None:
+                   dist_bucket: Optional[torch.Tensor] = None, chunk: int = 0,
+                   sink: Optional[torch.Tensor] = None) -> None:
     """Causal attention of prompt portions with keys of size d, values of size dv, ``v_share`` key
     heads to a value head, optional window and capped scores; out [T, nh*dv] in the cache's type or
     float32.  ``tile_*`` list tiles of 16 queries (general kernel, float32 arithmetic), ``tile64_*``
@@ -730,8 +731,10 @@ def attn_prefill_x(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache:
     row dist_bucket[min(i - j, len(dist_bucket) - 1)] to the scaled score of query i and key j;
     ``sigmoid_weights``: a visible key weighs sigmoid(score + head_bias[h]) and nothing is normalised.
     With softmax these three are the general kernel's alone; with sigmoid weights the mma.sync kernel
-    has them too while dist_bucket has fewer than ATTN_MMA_X_MAX_DIST entries."""
-    _attn_extras(nh, head_bias, dist_bias, dist_bucket)
+    has them too while dist_bucket has fewer than ATTN_MMA_X_MAX_DIST entries.  ``chunk`` > 0: a query sees
+    only the keys of its own chunk of that many positions (chunks counted from position 0 of the
+    sequence); ``sink`` [nh] float32: exp(sink[h]) is added to the softmax denominator of head h."""
+    _attn_extras(nh, head_bias, dist_bias, dist_bucket, sink)
     _check(lib().gg_attn_prefill_x(_p(q), ctypes.c_longlong(q_stride), _p(kcache), _p(vcache), dtype_code(kcache.dtype),
                                    _p(block_tables), bt_stride, _p(cu_q_lens), _p(context_lens), _p(tile_seq),
                                    _p(tile_q0), num_tiles, _p(tile64_seq), _p(tile64_q0), num_tiles64, int(allow_mma),
@@ -739,11 +742,19 @@ def attn_prefill_x(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache:
                                    nh, nkv, d, dv, v_share, page_size, window, ctypes.c_float(scale),
                                    ctypes.c_float(softcap), int(keep_first), int(sigmoid_weights), _p(head_bias),
                                    _p(dist_bias), _p(dist_bucket),
-                                   dist_bucket.numel() - 1 if dist_bucket is not None else 0, _stream()))
+                                   dist_bucket.numel() - 1 if dist_bucket is not None else 0, int(chunk or 0), _p(sink),
+                                   _stream()))
 
 
-def _attn_extras(nh, head_bias, dist_bias, dist_bucket) -> None:
-    _cuda(head_bias, dist_bias, dist_bucket)
+def attn_mma_x_chunk_sink() -> bool:
+    """Whether the mma.sync kernels behind attn_prefill_x / attn_decode_x take ``chunk`` and ``sink``."""
+    return bool(lib().gg_attn_mma_x_chunk_sink())
+
+
+def _attn_extras(nh, head_bias, dist_bias, dist_bucket, sink=None) -> None:
+    _cuda(head_bias, dist_bias, dist_bucket, sink)
+    if sink is not None and (sink.dtype != torch.float32 or sink.numel() != nh):
+        raise KernelError("attention: the sink is float32 [heads]")
     if head_bias is not None and (head_bias.dtype != torch.float32 or head_bias.numel() != nh):
         raise KernelError("attention: the bias per head is float32 [heads]")
     if dist_bias is not None and (dist_bias.dtype != torch.float32 or dist_bias.dim() != 2 or dist_bias.shape[1] != nh
@@ -757,9 +768,10 @@ def attn_decode_x(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache: 
                   out: torch.Tensor, nh: int, nkv: int, d: int, dv: int, v_share: int, page_size: int, window: int,
                   scale: float, softcap: float, allow_mma: bool = True, keep_first: int = 0,
                   sigmoid_weights: bool = False, head_bias: Optional[torch.Tensor] = None,
-                  dist_bias: Optional[torch.Tensor] = None, dist_bucket: Optional[torch.Tensor] = None) -> None:
+                  dist_bias: Optional[torch.Tensor] = None, dist_bucket: Optional[torch.Tensor] = None,
+                  chunk: int = 0, sink: Optional[torch.Tensor] = None) -> None:
     """The same for single decoded tokens, split over the context and merged."""
-    _attn_extras(nh, head_bias, dist_bias, dist_bucket)
+    _attn_extras(nh, head_bias, dist_bias, dist_bucket, sink)
     if part_o.numel() < n_dec * nh * num_splits * dv or part_ml.numel() < n_dec * nh * num_splits * 2:
         raise KernelError("attn_decode_x: scratch too small")
     _check(lib().gg_attn_decode_x(_p(q), ctypes.c_longlong(q_stride), _p(kcache), _p(vcache), dtype_code(kcache.dtype),
@@ -769,7 +781,7 @@ def attn_decode_x(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache: 
                                   v_share, page_size, window, ctypes.c_float(scale), ctypes.c_float(softcap),
                                   int(allow_mma), int(keep_first), int(sigmoid_weights), _p(head_bias), _p(dist_bias),
                                   _p(dist_bucket), dist_bucket.numel() - 1 if dist_bucket is not None else 0,
-                                  _stream()), 2)
+                                  int(chunk or 0), _p(sink), _stream()), 2)
 
 
 def diff_combine(maps: torch.Tensor, out: torch.Tensor, lam: float, eps: float, post: float, heads: int,
@@ -976,3 +988,134 @@ def sigmoid_gate(a: torch.Tensor, gate: torch.Tensor, out: torch.Tensor) -> None
         raise KernelError("sigmoid_gate: float32 values, gate and result of the activation type and one shape")
     _check(lib().gg_sigmoid_gate(_p(a), _p(gate), ctypes.c_longlong(gate.stride(0)), _p(out), a.shape[0], a.shape[1],
                                  dtype_code(out.dtype), _stream()))
+
+
+# ---------------------------------------------------------------- normed heads, rotated latent parts, gates
+def qkv_norm_rope_write(qkv: torch.Tensor, positions: torch.Tensor, slot_mapping: Optional[torch.Tensor],
+                        inv_freq: Optional[torch.Tensor], magnitude: float, q_weight: Optional[torch.Tensor],
+                        k_weight: Optional[torch.Tensor], eps: float, v_unit: bool, v_first: Optional[torch.Tensor],
+                        mix: int, lam: float, kcache: Optional[torch.Tensor], vcache: Optional[torch.Tensor], nh: int,
+                        nkv: int, d: int, nv: int, dv: int, page_size: int, interleaved: bool = False,
+                        write_cache: bool = True) -> None:
+    """Rows [nh*d | nkv*d | nv*dv] of qkv: every q and k head divided by its root mean square and
+    multiplied by q_weight / k_weight (float32 [d]; None: no norm), then rotated (the first
+    2 * len(inv_freq) values; cosines and sines times ``magnitude``): q in place, k to kcache.  Every v
+    head divided by its root mean square if ``v_unit``; ``mix`` 1: the result is also stored in v_first
+    (float32 [T, nv*dv]); 2: it is blended (1 - lam) v + lam v_first; then v goes to vcache."""
+    _cuda(positions, slot_mapping, inv_freq, q_weight, k_weight, v_first, kcache, vcache)
+    width = (nh + nkv) * d + nv * dv
+    if qkv.stride(1) != 1 or qkv.shape[1] < width:
+        raise KernelError("qkv_norm_rope_write: rows are not contiguous or too short")
+    if inv_freq is not None and inv_freq.dtype != torch.float64:
+        raise KernelError("qkv_norm_rope_write: inverse frequencies must be float64")
+    for w in (q_weight, k_weight):
+        if w is not None and (w.dtype != torch.float32 or w.numel() != d):
+            raise KernelError("qkv_norm_rope_write: a norm weight is float32 [head size]")
+    if v_first is not None and (v_first.dtype != torch.float32 or v_first.numel() < qkv.shape[0] * nv * dv):
+        raise KernelError("qkv_norm_rope_write: the first layer's values are float32 [T, nv * dv]")
+    if kcache is not None and (kcache.dtype != qkv.dtype or vcache.dtype != qkv.dtype):
+        raise KernelError("qkv_norm_rope_write: cache and activations differ in dtype")
+    rot = 2 * inv_freq.numel() if inv_freq is not None else 0
+    _check(lib().gg_qkv_norm_rope_write(_p(qkv), ctypes.c_longlong(qkv.stride(0)), dtype_code(qkv.dtype), _p(positions),
+                                        _p(slot_mapping), _p(inv_freq), ctypes.c_float(magnitude), _p(q_weight),
+                                        _p(k_weight), ctypes.c_float(eps), int(v_unit), int(mix), ctypes.c_float(lam),
+                                        _p(v_first), _p(kcache), _p(vcache), qkv.shape[0], nh, nkv, d, nv, dv, rot,
+                                        page_size, int(interleaved), int(write_cache), _stream()))
+
+
+def latent_rope(src: torch.Tensor, k_col0: int, q_head: int, q_off: int, heads: int, positions: torch.Tensor,
+                inv_freq: torch.Tensor, magnitude: float, interleaved: bool, slot_mapping: Optional[torch.Tensor],
+                cache: Optional[torch.Tensor], qout: torch.Tensor, row: int, dst_col: int, write_cache: bool = True) -> None:
+    """The rotated parts of a latent attention: columns [k_col0, + rot) of src[t] (the key part all heads share) go,
+    rotated, to columns [dst_col, + rot) of the cache row (``row`` values) at slot_mapping[t]; columns
+    [h * q_head + q_off, + rot) (head h's query part) to columns [h * row + dst_col, + rot) of qout[t]."""
+    _cuda(positions, inv_freq, slot_mapping, cache)
+    rot = 2 * inv_freq.numel()
+    if src.stride(1) != 1 or qout.stride(1) != 1 or qout.dtype != src.dtype or inv_freq.dtype != torch.float64 \
+            or (cache is not None and (cache.dtype != src.dtype or cache.shape[-1] != row)):
+        raise KernelError("latent_rope: rows contiguous and of one dtype, float64 frequencies, cache rows of the given width")
+    _check(lib().gg_latent_rope(_p(src), ctypes.c_longlong(src.stride(0)), int(k_col0), int(q_head), int(q_off), heads, rot,
+                                _p(positions), _p(inv_freq), ctypes.c_float(magnitude), int(interleaved), _p(slot_mapping),
+                                _p(cache), _p(qout), ctypes.c_longlong(qout.stride(0)), int(row), int(dst_col),
+                                int(write_cache), dtype_code(src.dtype), src.shape[0], _stream()))
+
+
+GATED_ACT_KINDS = {"relu": 0, "gelu_tanh": 1, "silu": 2}
+
+
+def gated_act(gate_up: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, kind: str) -> None:
+    """out[t, i] = act(gate_up[t, i] + bias[i]) * (gate_up[t, I + i] + bias[I + i]); bias float32 [2I] or None."""
+    _cuda(gate_up, bias, out)
+    T, I = out.shape
+    if gate_up.shape != (T, 2 * I) or gate_up.dtype != out.dtype or kind not in GATED_ACT_KINDS \
+            or (bias is not None and (bias.dtype != torch.float32 or bias.numel() != 2 * I)):
+        raise KernelError(f"gated_act: [T, 2I] in, [T, I] out of one dtype, float32 bias [2I], kind one of {sorted(GATED_ACT_KINDS)}")
+    _check(lib().gg_gated_act(_p(gate_up), _p(bias), _p(out), T, I, GATED_ACT_KINDS[kind], dtype_code(out.dtype), _stream()),
+           -(-T // 65535))
+
+
+def gate_mul(a: torch.Tensor, gate: torch.Tensor) -> None:
+    """a *= sigmoid(gate) in place: a [T, W] contiguous, gate a column view [T, W] of the same dtype."""
+    _cuda(a)
+    if gate.dtype != a.dtype or gate.stride(1) != 1 or gate.shape != a.shape:
+        raise KernelError("gate_mul: values and gate of one dtype and shape")
+    _check(lib().gg_gate_mul(_p(a), _p(gate), ctypes.c_longlong(gate.stride(0)), a.shape[0], a.shape[1],
+                             dtype_code(a.dtype), _stream()))
+
+
+def gate_norm_add(resid: torch.Tensor, y: torch.Tensor, y_bias: Optional[torch.Tensor], gate: Optional[torch.Tensor],
+                  gate_bias: Optional[torch.Tensor], weight: torch.Tensor, eps: float) -> None:
+    """resid += rmsnorm((y + y_bias) * sigmoid(gate + gate_bias)) * weight: resid float32 [T, H], y and gate
+    (a column view) of the activation type, the biases and the weight float32 [H]; gate None: no gate."""
+    _cuda(resid, y, y_bias, gate_bias, weight)
+    T, H = y.shape
+    if resid.dtype != torch.float32 or resid.shape != y.shape or weight.dtype != torch.float32 or weight.numel() != H:
+        raise KernelError("gate_norm_add: float32 residual of the input's shape, float32 weight of its width")
+    if gate is not None and (gate.dtype != y.dtype or gate.stride(1) != 1 or gate.shape != y.shape):
+        raise KernelError("gate_norm_add: the gate has the input's dtype and shape")
+    for b in (y_bias, gate_bias):
+        if b is not None and (b.dtype != torch.float32 or b.numel() != H):
+            raise KernelError("gate_norm_add: biases are float32 of the input's width")
+    _check(lib().gg_gate_norm_add(_p(resid), _p(y), _p(y_bias), _p(gate),
+                                  ctypes.c_longlong(gate.stride(0) if gate is not None else 0), _p(gate_bias), _p(weight),
+                                  dtype_code(y.dtype), T, H, ctypes.c_float(eps), _stream()))
+
+
+# ---------------------------------------------------------------- matrix memory with exponential gates
+def mlstm_gates(zi: torch.Tensor, zf: torch.Tensor, bias_i: Optional[torch.Tensor], bias_f: Optional[torch.Tensor],
+                cap: float, m_state: torch.Tensor, cu_q_lens: torch.Tensor, context_lens: torch.Tensor,
+                state_slots: torch.Tensor, num_seqs: int, heads: int, beta: torch.Tensor, decay: torch.Tensor,
+                m_out: torch.Tensor) -> None:
+    """i = cap tanh((zi + bias_i) / cap), f = logsigmoid(cap tanh((zf + bias_f) / cap)); per sequence and head
+    m_t = max(f_t + m_{t-1}, i_t) from m_state [slots, heads] (0 for a new sequence), which is moved on;
+    beta = exp(i - m_t), decay = exp(f + m_{t-1} - m_t), m_out = m_t, all float32 [T, heads].  zi and zf may
+    be column views of one float32 buffer."""
+    _cuda(bias_i, bias_f, m_state, beta, decay, m_out)
+    if zi.dtype != torch.float32 or zf.dtype != torch.float32 or zi.stride(1) != 1 or zf.stride(1) != 1 \
+            or m_state.dtype != torch.float32 or m_state.shape[-1] != heads:
+        raise KernelError("mlstm_gates: float32 gate rows, m_state float32 [slots, heads]")
+    _check(lib().gg_mlstm_gates(_p(zi), ctypes.c_longlong(zi.stride(0)), _p(zf), ctypes.c_longlong(zf.stride(0)), _p(bias_i),
+                                _p(bias_f), ctypes.c_float(cap), _p(m_state), _p(cu_q_lens), _p(context_lens),
+                                _p(state_slots), num_seqs, heads, _p(beta), _p(decay), _p(m_out), _stream()))
+
+
+def mlstm_rows(x: torch.Tensor, heads: int, d: int, dv: int, dvp: int, qscale: float, out: torch.Tensor) -> None:
+    """Rows [q | k | v] of x (heads x d, heads x d, heads x dv) to float32 rows [q * qscale | k | per head: v, 1,
+    zeros up to dvp]."""
+    _cuda(out)
+    if x.stride(1) != 1 or out.dtype != torch.float32 or out.shape[1] != heads * (2 * d + dvp):
+        raise KernelError("mlstm_rows: contiguous rows in, float32 [T, heads * (2 d + dvp)] out")
+    _check(lib().gg_mlstm_rows(_p(x), ctypes.c_longlong(x.stride(0)), dtype_code(x.dtype), x.shape[0], heads, d, dv, dvp,
+                               ctypes.c_float(qscale), _p(out), _stream()))
+
+
+def mlstm_out(o_raw: torch.Tensor, m_row: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float,
+              floor: float, heads: int, dv: int, dvp: int, out: torch.Tensor) -> None:
+    """out[t, h] = unit_rms(o[:dv] / (max(|o[dv]|, exp(-m)) + floor)) * weight[h] * sigmoid(gate[t, h]); o = o_raw[t, h]
+    (dvp values: column dv is the normaliser's dot product), gate a column view [T, heads*dv] of out's dtype."""
+    _cuda(o_raw, m_row, weight, out)
+    if gate.stride(1) != 1 or gate.dtype != out.dtype or weight.dtype != torch.float32 or weight.numel() != heads * dv:
+        raise KernelError("mlstm_out: gate rows contiguous and of the output's dtype, float32 weight [heads * dv]")
+    _check(lib().gg_mlstm_out(_p(o_raw), _p(m_row), _p(gate), ctypes.c_longlong(gate.stride(0)), dtype_code(out.dtype),
+                              _p(weight), ctypes.c_float(eps), ctypes.c_float(floor), out.shape[0], heads, dv, dvp, _p(out),
+                              _stream()))

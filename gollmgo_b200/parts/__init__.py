@@ -1,5 +1,5 @@
 from . import (attention, block, diff_attention, feed_forward, gated_delta, latent_attention, moe, norm,     # registers the built-in parts
-               parallel_mixer, position, sigmoid_attention, ssm, token_shift)
+               mlstm, normed_attention, parallel_mixer, position, sigmoid_attention, ssm, token_shift)
 from .context import BuildContext, QueryTiles, StepFacts, Workspace
 from .linear import linear, set_matmul_precision
 from .model import DecoderModel, build_model, manifest_for_config

@@ -126,6 +126,7 @@ class Attention:
 
     v_share = 1                  # consecutive key heads that read one value head
     bias = False                 # q, k, v and o have biases (local name + ".b")
+    extras = False               # a subclass with options that only the kernels of the general path take
 
     def __init__(self, spec, ctx):
         self.ctx = ctx
@@ -145,7 +146,7 @@ class Attention:
         self.names = tuple(spec.get("names") or ("q_proj.weight", "k_proj.weight", "v_proj.weight", "o_proj.weight"))
         self.out_buffer = spec.get("out_buffer") or "mixer_out"
         self.nv = self.nkv // self.v_share
-        self.general = (self.dv != self.d or self.softcap > 0 or self.v_share > 1 or self.bias
+        self.general = (self.dv != self.d or self.softcap > 0 or self.v_share > 1 or self.bias or self.extras
                         or float(getattr(self.position, "magnitude", 1.0)) != 1.0)
         self.qkv_width = (self.nh + self.nkv) * self.d + self.nv * self.dv
         self.qkv_bias = None

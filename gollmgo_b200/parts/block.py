@@ -8,6 +8,10 @@ and returns its own pending delta.
 
 "post_norm": x += s1 * norm(mixer(x)); x += s2 * norm(ffn(x)): the norm on the
 sublayer's output, an optional per-channel scale, the sublayers reading x itself.
+
+"sandwich": x += norm_b(gate(h) * mixer(h)), h = norm_a(x), and the same for the
+feed-forward: a norm before and after every sublayer, and between them an optional
+learned gate sigmoid(W h + b) per channel on the sublayer's result.
 """
 from __future__ import annotations
 
@@ -15,7 +19,7 @@ import torch
 
 from ..csrc import ops
 from ..weights import WeightSpec
-from .linear import NextNorm, NormedRows
+from .linear import NextNorm, NormedRows, linear
 from .registry import register_block
 
 
@@ -172,6 +176,76 @@ class ParallelBlock:
         return None
 
 
+class SandwichBlock:
+    """x += norm1b(g1 * mixer(h)) with h = norm1(x) and g1 = sigmoid(W1 h + b1); then the same with norm2, the
+    feed-forward, W2, b2 and norm2b.  norm1 and norm2 are the layer's two norms; the norms on the results (RMS norms
+    with a weight) and the gates are the block's own tensors, under the layer's block prefix.  A layer without a
+    feed-forward stops after the first line.  params: eps, gated (bool: the gates exist), post_names (names of the
+    two result norms), gate_names (names of the two gate weights; a bias is that name + ".b").
+
+    The gate's product reads the same rows as the sublayer.  Gate, norm and the add to the float32 stream are one
+    kernel (csrc/layernorm.cu), which also adds a bias that the sublayer's last product left in ``deferred_bias``."""
+
+    def __init__(self, layer_spec, mixer, feed_forward, mixer_norm, ffn_norm, ctx):
+        self.mixer, self.feed_forward = mixer, feed_forward
+        self.mixer_norm, self.ffn_norm = mixer_norm, ffn_norm
+        self.ctx = ctx
+        self.hidden = mixer_norm.size
+        p = layer_spec.block
+        self.eps = float(p["eps"])
+        self.gated = bool(p.get("gated", True))
+        self.post_names = tuple(p.get("post_names", ("norm1b", "norm2b")))
+        self.gate_names = tuple(p.get("gate_names", ("rg1", "rg2")))
+        if feed_forward is not None and ffn_norm is None:
+            raise ValueError("a sandwich block with a feed-forward needs the norm before it")
+        ctx.workspace.reserve("normed", ctx.max_tokens * self.hidden, ctx.act_dtype)
+        if self.gated:
+            ctx.workspace.reserve("resid_gate", ctx.max_tokens * self.hidden, ctx.act_dtype)
+        self.post_w = [None, None]
+        self.gate_w = [None, None]
+        self.gate_b = [None, None]
+
+    def _count(self):
+        return 2 if self.feed_forward is not None else 1
+
+    def weights(self):
+        w = {}
+        for i in range(self._count()):
+            w[self.post_names[i]] = WeightSpec((self.hidden,))
+            if self.gated:
+                w[self.gate_names[i]] = WeightSpec((self.hidden, self.hidden))
+                w[self.gate_names[i] + ".b"] = WeightSpec((self.hidden,), init="normal")
+        return w
+
+    def load(self, get):
+        for i in range(self._count()):
+            self.post_w[i] = get(self.post_names[i]).to(torch.float32).contiguous()
+            if self.gated:
+                self.gate_w[i] = get(self.gate_names[i]).contiguous()
+                self.gate_b[i] = get(self.gate_names[i] + ".b").to(torch.float32).contiguous()
+
+    def _join(self, i, resid, h, y, part):
+        g = None
+        if self.gated:
+            g = linear(h, self.gate_w[i], self.ctx.workspace.get("resid_gate", h.shape[0], self.hidden))
+        ops.gate_norm_add(resid, y, getattr(part, "deferred_bias", None), g, self.gate_b[i], self.post_w[i], self.eps)
+
+    def forward(self, resid, delta, batch, cache, writes_cache=True):
+        T = resid.shape[0]
+        if isinstance(delta, ResidualRows):
+            delta = None
+        elif delta is not None and not torch.is_tensor(delta):
+            raise ValueError("a sandwich block cannot take the norm's input from the block before it")
+        h = self.ctx.workspace.get("normed", T, self.hidden)
+        self.mixer_norm.add_norm(resid, delta, h)
+        self._join(0, resid, h, self.mixer.forward(h, batch, cache, writes_cache), self.mixer)
+        if self.feed_forward is not None:
+            self.ffn_norm.add_norm(resid, None, h)
+            self._join(1, resid, h, self.feed_forward.forward(h, batch), self.feed_forward)
+        return None
+
+
 register_block("pre_norm", PreNormBlock)
+register_block("sandwich", SandwichBlock)
 register_block("parallel", ParallelBlock)
 register_block("post_norm", PostNormBlock)

@@ -16,15 +16,22 @@ class GatedMLP:
     """params: hidden_size, intermediate_size, activation, names (optional: the local names of the
     gate, up and down tensors; default the Llama checkpoint's).  Activations: "silu" = silu(gate) * up;
     "clamped_swish" = g * sigmoid(alpha * g) * (u + shift) with g = min(gate, limit) and u = clamp(up,
-    -limit, limit) (params limit, alpha = 1.702, shift = 1)."""
+    -limit, limit) (params limit, alpha = 1.702, shift = 1); "relu" and "gelu_tanh" = act(gate) * up.
+    ``bias``: the three products have biases (tensors name + ".b"); ``defer_output_bias``: the last one's is
+    left in ``deferred_bias`` for a block that adds it with the stream."""
 
     def __init__(self, spec, ctx):
         self.ctx = ctx
         self.hidden = int(spec["hidden_size"])
         self.inter = int(spec["intermediate_size"])
         act = spec.get("activation", "silu")
-        if act not in ("silu", "clamped_swish"):
-            raise ValueError(f"activation {act!r} is not supported (known: silu, clamped_swish)")
+        if act not in ("silu", "clamped_swish", "relu", "gelu_tanh"):
+            raise ValueError(f"activation {act!r} is not supported (known: silu, clamped_swish, relu, gelu_tanh)")
+        self.bias = bool(spec.get("bias", False))
+        if self.bias and act == "clamped_swish":
+            raise ValueError("the clamped activation takes no biases")
+        self.defer_bias = bool(spec.get("defer_output_bias", False))
+        self.b_gate_up = self.b_down = self.deferred_bias = None
         self.activation = act
         if act == "clamped_swish":
             self.limit = float(spec["limit"])
@@ -40,23 +47,31 @@ class GatedMLP:
 
     def weights(self):
         g, u, d = self.names
-        return {g: WeightSpec((self.inter, self.hidden)),
-                u: WeightSpec((self.inter, self.hidden)),
-                d: WeightSpec((self.hidden, self.inter))}
+        w = {g: WeightSpec((self.inter, self.hidden)),
+             u: WeightSpec((self.inter, self.hidden)),
+             d: WeightSpec((self.hidden, self.inter))}
+        if self.bias:
+            w.update({g + ".b": WeightSpec((self.inter,), init="normal"), u + ".b": WeightSpec((self.inter,), init="normal"),
+                      d + ".b": WeightSpec((self.hidden,), init="normal")})
+        return w
 
     def load(self, get):
         g, u = get(self.names[0]), get(self.names[1])
         dt = torch.float32 if torch.float32 in (g.dtype, u.dtype) else g.dtype
         self.w_gate_up = torch.cat([g.to(dt), u.to(dt)], dim=0).contiguous()
         self.w_down = get(self.names[2]).contiguous()
+        if self.bias:
+            self.b_gate_up = torch.cat([get(self.names[0] + ".b").float(), get(self.names[1] + ".b").float()]).contiguous()
+            self.b_down = get(self.names[2] + ".b").float().contiguous()
+            self.deferred_bias = self.b_down if self.defer_bias else None
 
     # the optional protocol of parts/linear.py: the first product can take a norm's unnormalised
     # input, the last one can do the residual add and prepare the next norm
     def takes_normed_rows(self, num_tokens):
-        return self.activation == "silu" and fuses_norms(num_tokens, self.w_gate_up, self.ctx.act_dtype)
+        return self.activation == "silu" and not self.bias and fuses_norms(num_tokens, self.w_gate_up, self.ctx.act_dtype)
 
     def fuses_next_norm(self, num_tokens):
-        return fuses_norms(num_tokens, self.w_down, self.ctx.act_dtype)
+        return not self.bias and fuses_norms(num_tokens, self.w_down, self.ctx.act_dtype)
 
     def forward(self, x, batch, then=None):
         T = x.shape[0]
@@ -68,6 +83,9 @@ class GatedMLP:
             else:
                 gu = linear(x, self.w_gate_up, ws.get("gate_up", T, 2 * self.inter))
                 ops.clamped_gate(gu, a, self.limit, self.alpha, self.shift)
+        elif self.bias or self.activation != "silu":
+            gu = linear(x, self.w_gate_up, ws.get("gate_up", T, 2 * self.inter))
+            ops.gated_act(gu, self.b_gate_up, a, self.activation)
         elif isinstance(x, NormedRows):
             ops.gemm_small_m(x.scaled, self.w_gate_up, a, gated=True, in_partials=x.partials,
                              hidden=x.hidden, eps=x.eps)
@@ -82,6 +100,11 @@ class GatedMLP:
             linear(x, self.w_gate_up, gu)
             ops.silu_mul(gu, a)
         y = ws.get("ffn_out", T, self.hidden)
+        if self.bias:
+            linear(a, self.w_down, y)
+            if not self.defer_bias:
+                ops.bias_add(y, self.b_down)
+            return y
         return linear(a, self.w_down, y, then)
 
 

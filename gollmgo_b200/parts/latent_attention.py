@@ -1,5 +1,12 @@
 """Latent attention: every head's keys and values are expanded from one low-rank row per token
-(the latent), which is all the cache keeps.  No position encoding.
+(the latent), which is all the cache keeps.  Without position encoding, or (``rot_dim`` > 0) with a
+rotated part: every query head has ``rot_dim`` more values [head_dim unrotated | rot_dim rotated], the
+down-projection has ``rot_dim`` more rows that are, rotated and not normed, one key part shared by all
+heads, and the score is the sum of both dot products.  The cache row is then [latent | rotated key part]
+and the query in the latent's space [Wuk_h^T q_h | rotated query part]: one dot product gives the score,
+and the values are still the row's first ``rank`` columns.  ``window``: a query sees itself and the
+window - 1 tokens before it (the cache group gives older pages back).  ``gate``: "head" (one sigmoid gate
+per head), "element" (one per output channel of the concatenated heads) or False.
 
     q = Wq x  (heads x dim);   c = rmsnorm(Wdkv x) * w  (rank);   k_h = Wuk_h c;   v_h = Wuv_h c
     out = Wo concat_h( sigmoid(Wg x)_h * softmax_j(scale q_h . k_hj) v_hj ),  j <= i
@@ -12,8 +19,9 @@ product each (csrc/grouped_gemm.cu; the second one applies the head's gate), the
 and its write to the cache one kernel (csrc/latent.cu).  q, the latent and the gates come from
 one product with the three weights stacked.
 
-params: hidden_size, num_heads, head_dim (of q and k), v_head_dim, kv_rank, scale, eps (of the
-latent's norm), gate (bool), names: dict of the tensors' local names.
+params: hidden_size, num_heads, head_dim (of q and k, the unrotated part), v_head_dim, kv_rank, scale, eps (of the
+latent's norm), gate (True = "head" | "element" | False), rot_dim, position (PartSpec of the rotated part; its
+``interleaved`` and ``magnitude`` are honoured), window, names: dict of the tensors' local names.
 """
 from __future__ import annotations
 
@@ -26,7 +34,7 @@ from ..csrc import ops
 from ..weights import WeightSpec
 from .attention import ATTN_POLICY, TILES_GENERAL, TILES_MMA, TILES_TC, context_tiles, decode_splits, TILE_KEYS, MAX_TILES
 from .linear import GEMM_POLICY, linear
-from .registry import register_mixer
+from .registry import build_position, register_mixer
 
 DEFAULT_NAMES = {"q": "q", "dkv": "dkv", "dkv_norm": "dkv.norm", "uk": "uk", "uv": "uv", "gate": "g", "o": "o"}
 RANK_ALIGN = 16          # the latent's rows are padded to a multiple of this in the cache (zeros)
@@ -48,32 +56,51 @@ class LatentAttention:
         self.rank = int(spec["kv_rank"])
         self.scale = float(spec["scale"])
         self.eps = float(spec["eps"])
-        self.gated = bool(spec.get("gate", True))
+        gate = spec.get("gate", True)
+        self.gate_kind = "head" if gate is True else (gate or None)
+        if self.gate_kind not in (None, "head", "element"):
+            raise ValueError(f"gate {gate!r} is not known (known: head, element)")
+        self.gated = self.gate_kind == "head"
         self.names = {**DEFAULT_NAMES, **(spec.get("names") or {})}
+        self.rot = int(spec.get("rot_dim") or 0)
+        self.window = spec.get("window") or None
+        self.position = build_position(spec["position"], ctx) if self.rot else None
+        if self.rot and (self.position.rope_table() is None or 2 * self.position.rope_table().numel() != self.rot):
+            raise ValueError(f"the rotated part of {self.rot} values needs a rotation of exactly that width")
+        self.qh = self.dim + self.rot                     # a query head: [dim unrotated | rot rotated]
         self.rank_p = -(-self.rank // RANK_ALIGN) * RANK_ALIGN
         # A latent wider than the attention kernels' head size (256) cannot be read as a head: such a layer
         # caches the expanded keys and values instead (heads x max(dim, vdim) values each, zero-padded to one
         # size) and runs as ordinary multi-head attention.  More cache, the same result.
         self.expanded = self.rank_p > 256
+        # the cache row and the query in the latent's space: the latent (padded), then the rotated part; in bfloat16 the
+        # row is widened to 64 or 128 values where that is all it takes to run on the tensor-core kernels
+        self.row = self.rank_p + -(-self.rot // 8) * 8
+        if self.rot and ctx.act_dtype == torch.bfloat16 and self.row <= 128 and ATTN_POLICY != "general":
+            self.row = 64 if self.row <= 64 else 128
+        if self.rot and (self.expanded or self.row > 256):
+            raise ValueError(f"a latent of {self.rank} values with a rotated part of {self.rot} is beyond what the attention "
+                             f"kernels take (256 values a row)")
         self.dmax = -(-max(self.dim, self.vdim) // 8) * 8
         if self.expanded and self.dmax > 256:
             raise ValueError(f"a latent of {self.rank} values with heads of {self.dim} / {self.vdim} values is beyond "
                              f"what the attention kernels take (256 for the latent or for the heads)")
         # columns of the stacked first product: q | latent | gates, each start a multiple of 8
         a8 = lambda n: -(-n // 8) * 8
-        self.col_c = a8(self.nh * self.dim)
-        self.col_g = self.col_c + a8(self.rank)
-        self.width1 = self.col_g + (a8(self.nh) if self.gated else 0)
+        self.col_c = a8(self.nh * self.qh)
+        self.col_g = self.col_c + a8(self.rank + self.rot)
+        self.gate_cols = {None: 0, "head": self.nh, "element": self.nh * self.vdim}[self.gate_kind]
+        self.width1 = self.col_g + a8(self.gate_cols)
         self.num_sms = torch.cuda.get_device_properties(ctx.device).multi_processor_count \
             if ctx.device.type == "cuda" else 148
         ws, T = ctx.workspace, ctx.max_tokens
         ws.reserve("lat_proj", T * self.width1, ctx.act_dtype)
-        ws.reserve("lat_q", T * self.nh * self.rank_p, ctx.act_dtype)
-        ws.reserve("lat_o", T * self.nh * self.rank_p, ctx.act_dtype)
+        ws.reserve("lat_q", T * self.nh * self.row, ctx.act_dtype)
+        ws.reserve("lat_o", T * self.nh * self.row, ctx.act_dtype)
         ws.reserve("attn_out", T * self.nh * self.vdim, ctx.act_dtype)
         ws.reserve("mixer_out", T * self.hidden, ctx.act_dtype)
         # the attention as the kernels see it: kv heads, query heads per kv head, head size
-        self._nkv, self._group, self._d = (self.nh, 1, self.dmax) if self.expanded else (1, self.nh, self.rank_p)
+        self._nkv, self._group, self._d = (self.nh, 1, self.dmax) if self.expanded else (1, self.nh, self.row)
         self._ctas_per_split = self._nkv * -(-self._group // 16)
         self._cluster_cap = None
         if ctx.device.type == "cuda":
@@ -94,8 +121,8 @@ class LatentAttention:
 
     def cache_need(self):
         if self.expanded:
-            return PagedKVNeed(self.nh, self.dmax, None)
-        return PagedKVNeed(1, self.rank_p, None, shared_kv=True)
+            return PagedKVNeed(self.nh, self.dmax, self.window)
+        return PagedKVNeed(1, self.row, self.window, shared_kv=True)
 
     def _fast(self):
         return self.ctx.act_dtype == torch.bfloat16 and self._d in (64, 128) and ATTN_POLICY != "general"
@@ -110,7 +137,7 @@ class LatentAttention:
 
     def _splits(self, n_dec, max_context):
         return decode_splits(n_dec, self._ctas_per_split, self.num_sms, self._cluster_cap,
-                             context_tiles(max_context), self._tile_bytes)
+                             context_tiles(max_context, self.window), self._tile_bytes)
 
     def step_tags(self, facts):
         n = facts.num_seqs if facts.decode_only else 0
@@ -118,24 +145,24 @@ class LatentAttention:
 
     def weights(self):
         n, H = self.names, self.hidden
-        m = {n["q"]: WeightSpec((self.nh * self.dim, H)),
-             n["dkv"]: WeightSpec((self.rank, H)),
+        m = {n["q"]: WeightSpec((self.nh * self.qh, H)),
+             n["dkv"]: WeightSpec((self.rank + self.rot, H)),
              n["dkv_norm"]: WeightSpec((self.rank,)),
              n["uk"]: WeightSpec((self.nh * self.dim, self.rank)),
              n["uv"]: WeightSpec((self.nh * self.vdim, self.rank)),
              n["o"]: WeightSpec((H, self.nh * self.vdim))}
-        if self.gated:
-            m[n["gate"]] = WeightSpec((self.nh, H))
+        if self.gate_cols:
+            m[n["gate"]] = WeightSpec((self.gate_cols, H))
         return m
 
     def load(self, get):
         n = self.names
         q, dkv = get(n["q"]), get(n["dkv"])
         w = torch.zeros(self.width1, self.hidden, dtype=q.dtype, device=q.device)
-        w[:self.nh * self.dim] = q
-        w[self.col_c:self.col_c + self.rank] = dkv
-        if self.gated:
-            w[self.col_g:self.col_g + self.nh] = get(n["gate"])
+        w[:self.nh * self.qh] = q
+        w[self.col_c:self.col_c + self.rank + self.rot] = dkv
+        if self.gate_cols:
+            w[self.col_g:self.col_g + self.gate_cols] = get(n["gate"])
         self.w_in = w.contiguous()
         self.w_norm = get(n["dkv_norm"]).to(torch.float32).contiguous()
         # [heads, rank, dim]: the transpose of each head's key expansion, so that the query goes
@@ -157,7 +184,7 @@ class LatentAttention:
             if not self._fast():
                 t64 = t128 = None
             ops.attn_prefill(q, q_stride, kc, vc, bt, batch.bt_stride, batch.cu_q_lens, batch.context_lens,
-                             t16.seq, t16.q0, t16.count, o, nh, nkv, d, ps, 0, self.scale,
+                             t16.seq, t16.q0, t16.count, o, nh, nkv, d, ps, int(self.window or 0), self.scale,
                              t64.seq if t64 else None, t64.q0 if t64 else None, t64.count if t64 else 0,
                              allow_mma=t64 is not None,
                              tile128_seq=t128.seq if t128 else None, tile128_q0=t128.q0 if t128 else None,
@@ -169,7 +196,7 @@ class LatentAttention:
             splits = self._splits(n, longest)
             ops.attn_decode(q, q_stride, kc, vc, bt, batch.bt_stride, batch.cu_q_lens, batch.context_lens,
                             batch.dec_seqs, n, splits, ws.get("attn_part_o", 1, n * nh * splits * d),
-                            ws.get("attn_part_ml", 1, n * nh * splits * 2), o, nh, nkv, d, ps, 0, self.scale,
+                            ws.get("attn_part_ml", 1, n * nh * splits * 2), o, nh, nkv, d, ps, int(self.window or 0), self.scale,
                             allow_mma=self._fast())
 
     def _forward_expanded(self, x, batch, cache, writes_cache):
@@ -183,7 +210,7 @@ class LatentAttention:
         ops.latent_norm_write(proj, self.col_c, R, self.w_norm, self.eps, self._iota[:T], c)      # row t of c: the latent of token t
         qkv = ws.get("lat_qkv", T, 3 * nh * dm)
         qkv.zero_()                                           # the padding of every head stays zero
-        qkv.view(T, 3, nh, dm)[:, 0, :, :self.dim].copy_(proj[:, :nh * self.dim].view(T, nh, self.dim))
+        qkv.view(T, 3, nh, dm)[:, 0, :, :self.dim].copy_(proj[:, :nh * self.dim].view(T, nh, self.dim))      # (no rotated part here)
         ops.grouped_gemm(c, self.w_uk, qkv[:, nh * dm:], self.dim, R, nh, a_group_cols=0, o_group_cols=dm, n_padded=dm, rows=T)
         ops.grouped_gemm(c, self.w_uv, qkv[:, 2 * nh * dm:], self.vdim, R, nh, a_group_cols=0, o_group_cols=dm, n_padded=dm, rows=T)
         ops.rope_kv_write(qkv, batch.positions, batch.slot_mapping[group], None, kc, vc, nh, nh, dm, self.ctx.page_size,
@@ -195,6 +222,8 @@ class LatentAttention:
         a3.copy_(o.view(T, nh, dm)[:, :, :self.vdim])
         if self.gated:
             ops.head_gate(a, proj, self.col_g, nh)
+        elif self.gate_cols:
+            ops.gate_mul(a, proj[:, self.col_g:self.col_g + self.gate_cols])
         return linear(a, self.w_o, ws.get("mixer_out", T, self.hidden))
 
     def forward(self, x, batch, cache, writes_cache=True):
@@ -202,30 +231,41 @@ class LatentAttention:
             return self._forward_expanded(x, batch, cache, writes_cache)
         T, ws = x.shape[0], self.ctx.workspace
         kc, vc, group = cache
-        nh, R, Rp = self.nh, self.rank, self.rank_p
-        proj = ws.get("lat_proj", T, self.width1)
-        linear(x, self.w_in, proj)
+        nh, R, Rp, row = self.nh, self.rank, self.rank_p, self.row
+        proj = linear(x, self.w_in, ws.get("lat_proj", T, self.width1))
         if writes_cache:
             ops.latent_norm_write(proj, self.col_c, R, self.w_norm, self.eps, batch.slot_mapping[group], kc)
-        q = ws.get("lat_q", T, nh * Rp)
+        q = ws.get("lat_q", T, nh * row)
         lib = (T >= BMM_MIN_TOKENS and Rp == R and self.ctx.act_dtype == torch.bfloat16 and GEMM_POLICY != "tc")
-        if lib:
+        q_heads = proj[:, :nh * self.qh].view(T, nh, self.qh)[:, :, :self.dim].transpose(0, 1)      # [heads, T, dim]
+        if lib and row == R:
             # [heads, T, dim] @ [heads, dim, rank] -> [heads, T, rank], all three as views of the step's buffers
-            torch.bmm(proj[:, :nh * self.dim].view(T, nh, self.dim).transpose(0, 1), self.w_uk_t.transpose(1, 2),
-                      out=q.view(T, nh, Rp).transpose(0, 1))
+            torch.bmm(q_heads, self.w_uk_t.transpose(1, 2), out=q.view(T, nh, Rp).transpose(0, 1))
+        elif lib:
+            qv = q.view(T, nh, row)
+            qv[:, :, R:].zero_()                                   # the padding of every head's row stays zero
+            qv[:, :, :R].copy_(torch.bmm(q_heads, self.w_uk_t.transpose(1, 2)).transpose(0, 1))
         else:
-            ops.grouped_gemm(proj, self.w_uk_t, q, R, self.dim, nh, a_group_cols=self.dim, o_group_cols=Rp,
-                             n_padded=Rp, rows=T)
-        o = ws.get("lat_o", T, nh * Rp)
-        self._attend(q, nh * Rp, kc, vc, group, batch, o)
+            ops.grouped_gemm(proj, self.w_uk_t, q, R, self.dim, nh, a_group_cols=self.qh, o_group_cols=row,
+                             n_padded=row, rows=T)
+        if self.rot:
+            # the rotated parts: the shared key part into the cache row, every head's query part into its row of q
+            ops.latent_rope(proj, self.col_c + R, self.qh, self.dim, nh, batch.positions, self.position.rope_table(),
+                            float(getattr(self.position, "magnitude", 1.0)), self.position.interleaved,
+                            batch.slot_mapping[group], kc, q, row, Rp, writes_cache)
+        o = ws.get("lat_o", T, nh * row)
+        self._attend(q, nh * row, kc, vc, group, batch, o)
         a = ws.get("attn_out", T, nh * self.vdim)
         if lib:
-            torch.bmm(o.view(T, nh, Rp).transpose(0, 1), self.w_uv.transpose(1, 2), out=a.view(T, nh, self.vdim).transpose(0, 1))
+            torch.bmm(o.view(T, nh, row)[:, :, :R].transpose(0, 1), self.w_uv.transpose(1, 2),
+                      out=a.view(T, nh, self.vdim).transpose(0, 1))
             if self.gated:
                 ops.head_gate(a, proj, self.col_g, nh)
         else:
-            ops.grouped_gemm(o, self.w_uv, a, self.vdim, R, nh, a_group_cols=Rp, o_group_cols=self.vdim, rows=T,
+            ops.grouped_gemm(o, self.w_uv, a, self.vdim, R, nh, a_group_cols=row, o_group_cols=self.vdim, rows=T,
                              gate=proj if self.gated else None, gate_col0=self.col_g)
+        if self.gate_kind == "element":
+            ops.gate_mul(a, proj[:, self.col_g:self.col_g + self.gate_cols])
         return linear(a, self.w_o, ws.get("mixer_out", T, self.hidden))
 
 

@@ -47,7 +47,8 @@ class WeightSpec:
     kind: str = "float"          # "float" | "int"
     optional: bool = False       # may be absent (e.g. lm_head of a tied model)
     init: str = ""               # how random weights are drawn where the shape does not say: "normal" (a
-                                 # vector that is no norm weight), "taps" (rows of a short convolution)
+                                 # vector that is no norm weight), "taps" (rows of a short convolution),
+                                 # "fraction" (a blend factor between 0 and 1)
     free_dims: Tuple[int, ...] = ()   # dimensions whose size the checkpoint decides (``shape`` holds the size that
                                       # random weights are made with); the part reads the size from the tensor
 

@@ -32,6 +32,10 @@ def random_tensor(name: str, spec: WeightSpec, seed: int, device, dtype: torch.d
         t.normal_(0.0, 1.0 / spec.shape[-1], generator=gen)
         t[..., -1] += 1.0
         return t.to(dtype)
+    if spec.init == "fraction":                   # a blend factor: somewhere between the two things blended
+        t = torch.empty(spec.shape, dtype=torch.float32, device=device)
+        t.uniform_(0.2, 0.8, generator=gen)
+        return t.to(dtype)
     if len(spec.shape) <= 1 and spec.init != "normal":      # a norm's weight (a vector, or one number)
         t = torch.ones(spec.shape, dtype=torch.float32, device=device)
         if norm_jitter:
