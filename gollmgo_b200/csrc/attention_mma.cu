@@ -1087,7 +1087,8 @@ __global__ void __launch_bounds__(MMA_THREADS) attn_prefill_mma_x_kernel(AttnArg
   const int nrows = min(64, qlen - q0);
   const int first = qstart + q0;
   const int hi = first + nrows;
-  const int lo = a.window > 0 ? max(0, first - a.window + 1) : 0;
+  int lo = a.window > 0 ? max(0, first - a.window + 1) : 0;
+  if (!SIG && a.chunk > 0) lo = max(lo, (first / a.chunk) * a.chunk);      // the chunk of the tile's first row starts earliest
   const int kstart = (lo / MMA_BK) * MMA_BK;
   const int first_hi = SIG ? min(a.keep_first, lo) : 0;            // kept first keys behind the window: [0, first_hi)
   const int n0 = (first_hi + MMA_BK - 1) / MMA_BK;
@@ -1120,6 +1121,9 @@ __global__ void __launch_bounds__(MMA_THREADS) attn_prefill_mma_x_kernel(AttnArg
   load_q_frags<DK>(qf, [&](int r) { return wrow0 + r < nrows ? qbase + (size_t)r * a.q_stride : nullptr; });
   const bool row0_ok = wrow0 + g < nrows, row1_ok = wrow0 + g + 8 < nrows;
   const int wlast = first + min(wrow0 + 15, nrows - 1);
+  // chunked: the first key each of this thread's two rows sees, and the first any row of the warp sees
+  const int cs0 = a.chunk > 0 ? (max(pos0, 0) / a.chunk) * a.chunk : 0, cs1 = a.chunk > 0 ? (max(pos1, 0) / a.chunk) * a.chunk : 0;
+  const int wfirst = a.chunk > 0 ? ((first + wrow0) / a.chunk) * a.chunk : 0;
 
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
   float o[DV / 8][4];
@@ -1140,7 +1144,7 @@ __global__ void __launch_bounds__(MMA_THREADS) attn_prefill_mma_x_kernel(AttnArg
     const int st = it % STAGES;
     const unsigned ks = base + st * STAGE, vs = kv_same ? ks : ks + K_BYTES;
     const int kb = tile_kb(it), tlo = tile_lo(it), thi = tile_hi(it);
-    if (wrow0 < nrows && kb <= wlast) {
+    if (wrow0 < nrows && kb <= wlast && (SIG || kb + MMA_BK > wfirst)) {
       float s[8][4];
       qk_mma<DK, 8>(qf, ks, 0, s);
       unsigned p[4][4];
@@ -1178,7 +1182,7 @@ __global__ void __launch_bounds__(MMA_THREADS) attn_prefill_mma_x_kernel(AttnArg
             const int tk = kb + j * 8 + c2 + (e & 1);
             const int pos = (e & 2) ? pos1 : pos0;
             const bool ok = ((e & 2) ? row1_ok : row0_ok) && tk >= lo && tk <= pos &&
-                            (a.window <= 0 || tk > pos - a.window);
+                            (a.window <= 0 || tk > pos - a.window) && tk >= ((e & 2) ? cs1 : cs0);
             s[j][e] = ok ? score_exp2(s[j][e], scale, cap, inv_cap) : -INFINITY;
           }
         }
@@ -1194,6 +1198,11 @@ __global__ void __launch_bounds__(MMA_THREADS) attn_prefill_mma_x_kernel(AttnArg
   l[0] += __shfl_xor_sync(0xffffffffu, l[0], 2);
   l[1] += __shfl_xor_sync(0xffffffffu, l[1], 1);
   l[1] += __shfl_xor_sync(0xffffffffu, l[1], 2);
+  if (!SIG && a.sink) {                          // one more term of the denominator (the maxima are base-2 exponents)
+    const float sk = a.sink[h] * LOG2E;
+    if (m[0] != -INFINITY) l[0] += fast_exp2(fminf(sk - m[0], 120.f));
+    if (m[1] != -INFINITY) l[1] += fast_exp2(fminf(sk - m[1], 120.f));
+  }
   const float inv0 = SIG ? 1.f : l[0] > 0.f ? 1.f / l[0] : 0.f, inv1 = SIG ? 1.f : l[1] > 0.f ? 1.f / l[1] : 0.f;
   const size_t ostride = (size_t)a.nh * DV;
   const size_t at0 = (size_t)(t0 + q0 + wrow0 + g) * ostride + (size_t)h * DV, at1 = at0 + 8 * ostride;
@@ -1229,7 +1238,8 @@ __global__ void __launch_bounds__(MMA_THREADS) attn_decode_mma_x_kernel(AttnArgs
   const int nrows = min(16, G - g0);
   const int ctx = b >= 0 ? a.context_lens[b] : 0;
   const int t = b >= 0 ? a.cu_q_lens[b] : 0;
-  const int lo0 = a.window > 0 ? max(0, ctx - a.window) : 0;
+  int lo0 = a.window > 0 ? max(0, ctx - a.window) : 0;
+  if (!SIG && a.chunk > 0 && ctx > 0) lo0 = max(lo0, ((ctx - 1) / a.chunk) * a.chunk);    // the token's own chunk
   const int n = ctx - lo0;
   int chunk = (n + S - 1) / S;
   chunk = ((chunk + MMA_BK - 1) / MMA_BK) * MMA_BK;
@@ -1398,7 +1408,7 @@ static int prefill_x_go(const AttnArgs& a, int num_tiles, cudaStream_t stream) {
 
 // what the SIG kernels take: sigmoid weights (with or without the biases and kept first keys), and a
 // table over distances that fits beside the staged tiles
-bool attn_mma_x_chunk_sink_supported() { return false; }
+bool attn_mma_x_chunk_sink_supported() { return true; }
 
 bool attn_mma_x_sigmoid_supported(const AttnArgs& a) {
   return a.weights == 1 && a.dist_max >= 0 && a.dist_max < ATTN_MMA_X_MAX_DIST && (!a.dist_bias || a.dist_bucket);

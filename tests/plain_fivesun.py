@@ -53,6 +53,8 @@ def rotary_frequencies(rot):
 
 def rotate(x, positions, rot):
     """x [T, heads, size]: neighbouring channels (2i, 2i+1) of the first ``dims`` turn by position * f_i."""
+    if not rot:
+        return x
     f, mag = rotary_frequencies(rot)
     dims = int(rot["dims"])
     ang = positions[:, None].astype(np.float64) * f[None, :]
@@ -80,13 +82,6 @@ def causal_mask(T):
     return j <= i
 
 
-def mask_of(m, T):
-    mk = m.get("mask")
-    if not mk:
-        return causal_mask(T)
-    return chunk_mask(T, int(mk["size"])) if m["_mask_kind"] == "chunk" else window_mask(T, int(mk["size"]))
-
-
 def softmax_rows(scores, visible, sink=None):
     """Softmax over the visible keys of every row; ``sink`` (one number per row or None) is one more
     term of the denominator that has no value."""
@@ -112,8 +107,8 @@ def attention(h, w, p, m, eps, v_first=None):
     q = (h @ w[p + "q"].T).reshape(T, H, d)
     k = (h @ w[p + "k"].T).reshape(T, G, d)
     v = (h @ w[p + "v"].T).reshape(T, G, dv)
-    q = rotate(rms_norm(q, w[p + "q.norm"], eps), pos, m["rot"])
-    k = rotate(rms_norm(k, w[p + "k.norm"], eps), pos, m["rot"])
+    q = rotate(rms_norm(q, w[p + "q.norm"], eps), pos, m.get("rot"))
+    k = rotate(rms_norm(k, w[p + "k.norm"], eps), pos, m.get("rot"))
     v = unit_rms(v, eps)
     if m.get("v_mix") and v_first is not None:
         lam = float(w[p + "vmix"])
@@ -138,10 +133,10 @@ def latent_attention(h, w, p, m, eps):
     H, d, dr, dv, R = int(m["heads"]), int(m["dim"]), int(m["rot_dim"]), int(m["vdim"]), int(m["kv_rank"])
     pos = np.arange(T)
     q = (h @ w[p + "q"].T).reshape(T, H, d + dr)
-    q_flat, q_rot = q[..., :d], rotate(q[..., d:], pos, m["rot"])
+    q_flat, q_rot = q[..., :d], rotate(q[..., d:], pos, m.get("rot"))
     down = h @ w[p + "dkv"].T
     c = rms_norm(down[:, :R], w[p + "dkv.norm"], eps)
-    k_rot = rotate(down[:, None, R:], pos, m["rot"])[:, 0]          # [T, dr]
+    k_rot = rotate(down[:, None, R:], pos, m.get("rot"))[:, 0]          # [T, dr]
     k_flat = (c @ w[p + "uk"].T).reshape(T, H, d)
     v = (c @ w[p + "uv"].T).reshape(T, H, dv)
     visible = window_mask(T, int(m["mask"]["size"])) if m.get("mask") else causal_mask(T)

@@ -1,0 +1,592 @@
+"""Fivesun on the device against the plain implementation (tests/plain_fivesun.py): each mechanism alone
+(with weights and inputs made so that a chunk or a window that is one off, a sink that is left out, a lost
+far key or a lost state shows), then whole models replayed through bin/trace_run (whole prompts, the last
+tokens one by one, portions down to two tokens, mixed batches on a pool so small that pages and slots are
+used again), then greedy generation through the engine's entry point and scheduler."""
+import math
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import fivesun_tools as ft
+import plain_fivesun as P
+import trace_tools as tt
+from mixer_tools import MixerRun, bf, close, ctx_for, cuts_of, make_kit
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+TWO = [{"a": (0, 9), "b": (0, 2)}, {"a": (9, 10)}, {"b": (2, 19), "a": (10, 11)}, {"a": (11, 12), "b": (19, 20)},
+       {"a": (12, 60), "b": (20, 41)}, {"a": (60, 75)}]
+
+
+@pytest.fixture(scope="module")
+def kit(cuda_device):
+    return make_kit()
+
+
+def npw(w, prefix="p."):
+    return {prefix + k: v.double().numpy() for k, v in w.items()}
+
+
+def rope_spec(kit, rot, dim):
+    if rot is None:
+        return kit.parts.PartSpec("none")
+    from gollmgo_b200.config import RopeScaling
+    from gollmgo_b200.parts.position import YarnScaling
+    sc = rot.get("scaling")
+    scaling = None
+    if sc and "original" in sc:
+        scaling = YarnScaling(sc["factor"], sc["original"], sc["fast"], sc["slow"])
+    elif sc:
+        scaling = RopeScaling("linear", factor=sc["factor"])
+    return kit.parts.PartSpec("rope", {"head_dim": dim, "rotary_dim": rot["dims"], "theta": rot["base"], "scaling": scaling,
+                                       "interleaved": True})
+
+
+# ------------------------------------------------------------------ small kernels
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_gated_activation_gates_and_the_gated_norm(kit, dtype):
+    g = torch.Generator().manual_seed(0)
+    T, I, W = 11, 52, 100
+    gu, b = bf(torch.randn(T, 2 * I, generator=g) * 2), bf(torch.randn(2 * I, generator=g))
+    for kind, f in (("relu", lambda z: z.clamp(min=0)), ("silu", lambda z: z * torch.sigmoid(z)),
+                    ("gelu_tanh", lambda z: 0.5 * z * (1 + torch.tanh(math.sqrt(2 / math.pi) * (z + 0.044715 * z ** 3))))):
+        out = torch.empty(T, I, device="cuda", dtype=dtype)
+        kit.ops.gated_act(gu.cuda().to(dtype), b.float().cuda(), out, kind)
+        close(out, f(gu[:, :I] + b[:I]) * (gu[:, I:] + b[I:]), dtype, bf16=8e-3)
+    a, wide = bf(torch.randn(T, W, generator=g)), bf(torch.randn(T, W + 24, generator=g) * 3)
+    x = a.cuda().to(dtype)
+    kit.ops.gate_mul(x, wide.cuda().to(dtype)[:, 16:16 + W])
+    close(x, a * torch.sigmoid(wide[:, 16:16 + W]), dtype, bf16=8e-3)
+    # resid += rmsnorm((y + yb) * sigmoid(gate + gb)) * w
+    y, gate = bf(torch.randn(T, W, generator=g) * 4), bf(torch.randn(T, W, generator=g) * 2)
+    yb, gb, w = bf(torch.randn(W, generator=g)), bf(torch.randn(W, generator=g)), bf(1 + 0.2 * torch.randn(W, generator=g))
+    r0 = torch.randn(T, W, generator=g)
+    resid = r0.clone().cuda()
+    kit.ops.gate_norm_add(resid, y.cuda().to(dtype), yb.float().cuda(), gate.cuda().to(dtype), gb.float().cuda(), w.float().cuda(), 3e-6)
+    z = ((y + yb) * torch.sigmoid(gate + gb)).numpy()
+    close(resid, r0.double() + torch.from_numpy(P.rms_norm(z, w.numpy(), 3e-6)), torch.float32, f32=2e-6)
+
+
+# ------------------------------------------------------------------ attention with normed heads
+def att_weights(D, m, seed):
+    g = torch.Generator().manual_seed(seed)
+    r = lambda *s: torch.randn(*s, generator=g)
+    H, G, d, v = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    w = {"q": r(H * d, D) * 1.5 / D ** 0.5, "k": r(G * d, D) * 1.5 / D ** 0.5, "v": r(G * v, D) / D ** 0.5,
+         "q.norm": 1 + 0.2 * r(d), "k.norm": 1 + 0.2 * r(d), "sink": 1.0 + r(H), "g": r(H, D) / D ** 0.5,
+         "o": r(D, H * v) / (H * v) ** 0.5}
+    if m.get("v_mix"):
+        w["vmix"] = torch.tensor(0.4375)
+    return {k: bf(x) for k, x in w.items()}
+
+
+def att_mixer(kit, dtype, D, m, eps, page=16, v_mix=None, ctx=None, max_tokens=640):
+    return kit.parts.build_mixer(kit.parts.PartSpec("normed_attention", {
+        "hidden_size": D, "num_heads": m["heads"], "num_kv_heads": m["kv_heads"], "head_dim": m["dim"],
+        "v_head_dim": m["vdim"], "position": rope_spec(kit, m.get("rot"), m["dim"]), "scale": m["scale"], "eps": eps,
+        "chunk": (m.get("mask") or {}).get("size"), "v_mix": v_mix}), ctx or ctx_for(kit, dtype, page, max_tokens))
+
+
+# width, heads, kv heads, key size, value size, chunk, rotated dims, base, factor, page
+ATT_SHAPES = [(64, 4, 2, 32, 16, 24, 16, 10000.0, 2.0, 16), (96, 3, 1, 24, 40, 40, 24, 500000.0, None, 8),
+              (100, 6, 2, 12, 20, 7, 8, 10000.0, 1.5, 8), (72, 2, 2, 20, 12, None, 20, 10000.0, 3.0, 16),
+              (128, 2, 2, 64, 64, 100, 64, 1000000.0, 8.0, 8), (128, 4, 2, 128, 64, 128, 64, 1000000.0, 2.0, 32),
+              (128, 8, 2, 64, 128, 50, 32, 10000.0, None, 16), (96, 17, 1, 16, 16, 33, 16, 10000.0, None, 16)]
+
+
+def att_entry(shape):
+    D, H, G, d, v, chunk, dims, base, factor, page = shape
+    m = {"heads": H, "kv_heads": G, "dim": d, "vdim": v, "scale": 1.3 / math.sqrt(d), "rot": {"dims": dims, "base": base}}
+    if factor:
+        m["rot"]["scaling"] = {"factor": factor}
+    if chunk:
+        m["mask"] = {"size": chunk}
+    return D, m, page
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", ATT_SHAPES)
+def test_normed_attention_in_portions_and_token_by_token(kit, dtype, shape):
+    """Whole, in portions down to two tokens, token by token, and two requests in the same steps; the plain
+    implementation first shows that leaving the sink out, or a chunk one off, changes the result."""
+    D, m, page = att_entry(shape)
+    eps = 1e-5
+    w = att_weights(D, m, seed=21)
+    mixer = att_mixer(kit, dtype, D, m, eps, page)
+    assert set(mixer.weights()) == set(w)
+    mixer.load(lambda n: w[n].cuda().to(dtype))
+    g = torch.Generator().manual_seed(22)
+    xa, xb = bf(torch.randn(75, D, generator=g)), bf(torch.randn(41, D, generator=g))
+    wa = torch.from_numpy(P.attention(xa.numpy(), npw(w), "p.", m, eps)[0])
+    wb = torch.from_numpy(P.attention(xb.numpy(), npw(w), "p.", m, eps)[0])
+    no_sink = dict(npw(w), **{"p.sink": np.full(m["heads"], -50.0)})
+    assert np.abs(P.attention(xa.numpy(), no_sink, "p.", m, eps)[0] - wa.numpy()).max() > 0.05 * wa.abs().max()
+    if m.get("mask") and m["mask"]["size"] < 70:
+        off = dict(m, mask={"size": m["mask"]["size"] + 1})
+        assert np.abs(P.attention(xa.numpy(), npw(w), "p.", off, eps)[0] - wa.numpy()).max() > 0.05 * wa.abs().max()
+    tol = dict(f32=1e-4, bf16=4e-2)
+    run = MixerRun(kit, mixer, dtype, page)
+    close(run.feed(xa, [75], "whole"), wa, dtype, **tol)
+    close(run.feed(xa, cuts_of(75, [2, 3, 2, 17, 5, 2, 30]), "cut"), wa, dtype, **tol)
+    close(run.feed(xa, [1] * 75, "single"), wa, dtype, **tol)
+    got = MixerRun(kit, mixer, dtype, page).plan({"a": xa, "b": xb}, TWO)
+    close(got["a"], wa, dtype, **tol)
+    close(got["b"], wb, dtype, **tol)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_values_blend_with_the_first_layers(kit, dtype):
+    """Two layers of one model: the first leaves its normed values for the step, the second blends its own with
+    them before it caches them: checked in one step, in portions, and token by token through the cache."""
+    D, eps, page = 64, 1e-5, 16
+    m = {"heads": 4, "kv_heads": 2, "dim": 32, "vdim": 16, "scale": 0.2, "rot": {"dims": 16, "base": 10000.0},
+         "mask": {"size": 24}, "v_mix": True}
+    w1, w2 = att_weights(D, m, 31), att_weights(D, m, 32)
+    ctx = ctx_for(kit, dtype, page)
+    first, second = att_mixer(kit, dtype, D, m, eps, page, "first", ctx), att_mixer(kit, dtype, D, m, eps, page, "blend", ctx)
+    first.load(lambda n: w1[n].cuda().to(dtype))
+    second.load(lambda n: w2[n].cuda().to(dtype))
+    g = torch.Generator().manual_seed(33)
+    x1, x2 = bf(torch.randn(60, D, generator=g)), bf(torch.randn(60, D, generator=g))
+    _, v1 = P.attention(x1.numpy(), npw(w1), "p.", m, eps)
+    want = torch.from_numpy(P.attention(x2.numpy(), npw(w2), "p.", m, eps, v_first=v1)[0])
+    alone = torch.from_numpy(P.attention(x2.numpy(), npw(w2), "p.", m, eps)[0])
+    assert (want - alone).abs().max() > 0.1 * want.abs().max()
+    for cuts in ([60], cuts_of(60, [2, 7, 3, 19]), [1] * 60):
+        ra, rb = MixerRun(kit, first, dtype, page), MixerRun(kit, second, dtype, page)
+        outs, at = [], 0
+        for c in cuts:
+            ra.step({"s": x1[at:at + c]})
+            outs.append(rb.step({"s": x2[at:at + c]})["s"])
+            at += c
+        close(torch.cat(outs), want, dtype, f32=1e-4, bf16=4e-2)
+
+
+TAGS = 4
+
+
+def loud_case(kind, shape, n=300):
+    """Inputs in which a few keys can be made to stand out: the last 2 * TAGS input channels are tags.  A key tag
+    drives one channel of every key head far above the others (after the head's norm it is about sqrt(size)), a
+    query tag the same channel of every query head; that channel lies past the rotated ones, or on the slowest
+    pair of a large base.  A query with tag t then gives the key with tag t nearly all its weight."""
+    D, m, page = shape
+    C = D - 2 * TAGS
+    g = torch.Generator().manual_seed(41)
+    x = torch.zeros(n, D)
+    x[:, :C] = torch.randn(n, C, generator=g)
+    return D, m, page, C, g, x
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", [(96, 4, 2, 32, 16, 24, 16, 1e6, 2.0, 16), (128, 2, 2, 64, 64, 100, 32, 1e6, None, 8),
+                                   (104, 6, 3, 24, 20, 7, 8, 1e6, 1.5, 8), (128, 4, 1, 128, 128, 64, 64, 1e6, 2.0, 16)])
+def test_normed_attention_at_the_edges_of_chunks(kit, dtype, shape):
+    """Queries whose one loud key is the first of their chunk, the last of the chunk before, at both sides of a
+    page border, and far back inside a long chunk; in one step, in portions down to two tokens with the last forty
+    tokens one by one, and as two requests in mixed steps."""
+    D, m, page = att_entry(shape)
+    D, m, page, C, g, x = loud_case("att", (D, m, page))
+    H, G, d, v, ch = m["heads"], m["kv_heads"], m["dim"], m["vdim"], m["mask"]["size"]
+    m["scale"] = 12.0 / d                                    # a loud pair scores about 12, a quiet one about 12 / sqrt(d)
+    eps = 1e-5
+    w = att_weights(D, m, seed=42)
+    q, k = torch.zeros(H, d, D), torch.zeros(G, d, D)
+    q[:, :d - TAGS, :C] = torch.randn(H, d - TAGS, C, generator=g) / C ** 0.5
+    k[:, :d - TAGS, :C] = torch.randn(G, d - TAGS, C, generator=g) / C ** 0.5
+    for t in range(TAGS):
+        q[:, d - TAGS + t, C + TAGS + t] = 40.0
+        k[:, d - TAGS + t, C + t] = 40.0
+    w.update({"q": bf(q.reshape(H * d, D)), "k": bf(k.reshape(G * d, D)), "q.norm": bf(torch.ones(d)), "k.norm": bf(torch.ones(d)),
+              "sink": bf(torch.full((H,), 2.0))})
+    n = x.shape[0]
+    first = [c for c in range(0, n, ch)]                     # first positions of the chunks
+    # keys: the first token of a late chunk, the last token of the chunk before it, a key at a page border, a key far back
+    c2 = first[len(first) // 2]
+    keys = [c2, c2 - 1, (c2 // page) * page + page if (c2 // page) * page + page < c2 + ch else c2 + 1, first[-2] + 1]
+    asks = {}
+    def ask(qi, t):
+        if 0 < qi < n and qi > keys[t] and qi not in asks and qi not in keys:
+            asks[qi] = t
+    ask(min(c2 + ch - 1, n - 1), 0)      # the last query of the chunk sees its first key
+    ask(c2 + 1 if c2 + 1 not in keys else c2 + 2, 1)      # just over the border: the key before the chunk is gone
+    ask(min(keys[2] + 3, c2 + ch - 1), 2)
+    ask(min(first[-2] + ch - 1, n - 2), 3)
+    ask(n - 1, 3 if first[-1] <= keys[3] else 0)      # a decoded token
+    for t, kp in enumerate(keys):
+        x[kp, C + t] = 1.0
+    for qi, t in asks.items():
+        x[qi, C + TAGS + t] = 1.0
+    x = bf(x)
+    want = torch.from_numpy(P.attention(x.numpy(), npw(w), "p.", m, eps)[0])
+    def differs(size):
+        other = P.attention(x.numpy(), npw(w), "p.", dict(m, mask={"size": size}), eps)[0]
+        return set(np.nonzero(np.abs(other - want.numpy()).max(1) > 0.2 * np.abs(want.numpy()).max(1))[0].tolist())
+    asked = set(asks)
+    assert asked & differs(ch + 1) and asked & differs(ch - 1), "a chunk that is one off does not show at the asking rows"
+    mixer = att_mixer(kit, dtype, D, m, eps, page)
+    mixer.load(lambda nm: w[nm].cuda().to(dtype))
+    tol = dict(f32=2e-4, bf16=5e-2)
+    run = MixerRun(kit, mixer, dtype, page)
+    close(run.feed(x, [n], "whole"), want, dtype, **tol)
+    close(run.feed(x, cuts_of(n - 40, [2, 3, 2, 17, 5, 2, 30, 64]) + [1] * 40, "cut"), want, dtype, **tol)
+    close(run.feed(x, cuts_of(n, [33, 7, 65]), "odd"), want, dtype, **tol)
+    xb = x[:130]
+    wb = torch.from_numpy(P.attention(xb.numpy(), npw(w), "p.", m, eps)[0])
+    plan = [{"a": (0, 50), "b": (0, 3)}, {"a": (50, 51), "b": (3, 90)}, {"a": (51, 200), "b": (90, 91)},
+            {"a": (200, 201), "b": (91, 92)}, {"a": (201, n), "b": (92, 130)}]
+    got = MixerRun(kit, mixer, dtype, page).plan({"a": x, "b": xb}, plan)
+    close(got["a"], want, dtype, **tol)
+    close(got["b"], wb, dtype, **tol)
+
+
+# ------------------------------------------------------------------ latent attention with a rotated part
+def lat_weights(D, m, seed):
+    g = torch.Generator().manual_seed(seed)
+    r = lambda *s: torch.randn(*s, generator=g)
+    H, d, dr, v, R = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
+    w = {"q": r(H * (d + dr), D) * 1.5 / D ** 0.5, "dkv": r(R + dr, D) * 1.5 / D ** 0.5, "dkv.norm": 1 + 0.2 * r(R),
+         "uk": r(H * d, R) / R ** 0.5, "uv": r(H * v, R) / R ** 0.5, "g": r(H * v, D) / D ** 0.5,
+         "o": r(D, H * v) / (H * v) ** 0.5}
+    return {k: bf(x) for k, x in w.items()}
+
+
+def lat_mixer(kit, dtype, D, m, eps, page=16, max_tokens=640):
+    return kit.parts.build_mixer(kit.parts.PartSpec("latent_attention", {
+        "hidden_size": D, "num_heads": m["heads"], "head_dim": m["dim"], "v_head_dim": m["vdim"], "kv_rank": m["kv_rank"],
+        "scale": m["scale"], "eps": eps, "gate": "element", "rot_dim": m["rot_dim"],
+        "position": rope_spec(kit, m["rot"], m["rot_dim"]), "window": (m.get("mask") or {}).get("size")}),
+        ctx_for(kit, dtype, page, max_tokens))
+
+
+# width, heads, unrotated, rotated, value size, rank, window, base, (factor, original, fast, slow), page
+LAT_SHAPES = [(64, 3, 16, 8, 24, 24, 20, 10000.0, (4.0, 64, 16.0, 1.0), 16), (128, 4, 32, 16, 32, 48, 150, 1e6, (2.0, 128, 32.0, 2.0), 8),
+              (100, 5, 12, 4, 20, 40, 5, 5000.0, None, 8), (72, 1, 24, 12, 16, 30, None, 10000.0, (8.0, 32, 8.0, 1.0), 16),
+              (192, 4, 64, 32, 64, 96, 100, 1e6, (4.0, 256, 32.0, 1.0), 32), (96, 2, 16, 16, 16, 130, 33, 10000.0, None, 16),
+              (96, 6, 24, 8, 24, 56, 70, 10000.0, (3.0, 100, 20.0, 1.0), 16)]
+
+
+def lat_entry(shape):
+    D, H, d, dr, v, R, window, base, yarn, page = shape
+    rot = {"dims": dr, "base": base}
+    if yarn:
+        rot["scaling"] = dict(zip(("factor", "original", "fast", "slow"), yarn))
+    m = {"heads": H, "dim": d, "rot_dim": dr, "vdim": v, "kv_rank": R, "scale": 1.2 / math.sqrt(d + dr), "rot": rot}
+    if window:
+        m["mask"] = {"size": window}
+    return D, m, page
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", LAT_SHAPES)
+def test_latent_attention_in_portions_and_token_by_token(kit, dtype, shape):
+    D, m, page = lat_entry(shape)
+    eps = 1e-5
+    w = lat_weights(D, m, seed=51)
+    mixer = lat_mixer(kit, dtype, D, m, eps, page)
+    assert set(mixer.weights()) == set(w)
+    mixer.load(lambda n: w[n].cuda().to(dtype))
+    g = torch.Generator().manual_seed(52)
+    xa, xb = bf(torch.randn(75, D, generator=g)), bf(torch.randn(41, D, generator=g))
+    wa = torch.from_numpy(P.latent_attention(xa.numpy(), npw(w), "p.", m, eps))
+    wb = torch.from_numpy(P.latent_attention(xb.numpy(), npw(w), "p.", m, eps))
+    flat = dict(m, rot={"dims": m["rot_dim"], "base": m["rot"]["base"]})
+    if "scaling" in m["rot"]:
+        assert np.abs(P.latent_attention(xa.numpy(), npw(w), "p.", flat, eps) - wa.numpy()).max() > 0.02 * wa.abs().max()
+    tol = dict(f32=1e-4, bf16=4e-2)
+    run = MixerRun(kit, mixer, dtype, page)
+    close(run.feed(xa, [75], "whole"), wa, dtype, **tol)
+    close(run.feed(xa, cuts_of(75, [2, 3, 2, 17, 5, 2, 30]), "cut"), wa, dtype, **tol)
+    close(run.feed(xa, [1] * 75, "single"), wa, dtype, **tol)
+    got = MixerRun(kit, mixer, dtype, page).plan({"a": xa, "b": xb}, TWO)
+    close(got["a"], wa, dtype, **tol)
+    close(got["b"], wb, dtype, **tol)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", [LAT_SHAPES[0], LAT_SHAPES[1], LAT_SHAPES[2], LAT_SHAPES[4], LAT_SHAPES[6]])
+def test_latent_attention_at_the_edges_of_the_window(kit, dtype, shape):
+    """One loud key per asking query: the oldest inside the window, the first outside it, keys at both sides of a
+    page border; pages behind the window are given back while the request runs.  The loud channel is a channel of
+    the latent that only the tag drives and that every head's key expansion maps to one unrotated key channel."""
+    D, m, page = lat_entry(shape)
+    D, m, page, C, g, x = loud_case("lat", (D, m, page), n=330)
+    H, d, dr, v, R, W = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"], m["mask"]["size"]
+    m["scale"] = 14.0 / (12.0 * math.sqrt(R))               # a loud pair scores about 14, a quiet one about 1.5
+    eps = 1e-5
+    w = lat_weights(D, m, seed=53)
+    q = w["q"].reshape(H, d + dr, D).clone()
+    dkv, uk = w["dkv"].clone(), w["uk"].reshape(H, d, R).clone()
+    q[:, :, C:], dkv[:, C:] = 0, 0
+    q[:, :TAGS], dkv[:TAGS], uk[:, :TAGS], uk[:, :, :TAGS] = 0, 0, 0, 0
+    for t in range(TAGS):
+        dkv[t, C + t] = 60.0                                # latent channel t: after the norm about sqrt(R)
+        uk[:, t, t] = 1.0                                    # ... becomes key channel t of every head
+        q[:, t, C + TAGS + t] = 12.0
+    w.update({"q": bf(q.reshape(H * (d + dr), D)), "dkv": bf(dkv), "uk": bf(uk.reshape(H * d, R)), "dkv.norm": bf(torch.ones(R))})
+    n = x.shape[0]
+    keys = [3 * page - 1, 3 * page, 100 + page // 2, 6 * page]
+    asks = {}
+    def ask(qi, t):
+        if qi < n and qi > keys[t] and qi not in asks and qi not in keys:
+            asks[qi] = t
+    for t in range(TAGS):
+        ask(keys[t] + W - 1, t)          # the oldest key the query still sees
+        ask(keys[t] + W, t)              # one token later it is gone
+    for t, kp in enumerate(keys):
+        x[kp, C + t] = 1.0
+    for qi, t in asks.items():
+        x[qi, C + TAGS + t] = 1.0
+    x = bf(x)
+    want = torch.from_numpy(P.latent_attention(x.numpy(), npw(w), "p.", m, eps))
+    def differs(size):
+        other = P.latent_attention(x.numpy(), npw(w), "p.", dict(m, mask={"size": size}), eps)
+        return set(np.nonzero(np.abs(other - want.numpy()).max(1) > 0.2 * np.abs(want.numpy()).max(1))[0].tolist())
+    inside, outside = {qi for qi, t in asks.items() if qi - keys[t] == W - 1}, {qi for qi, t in asks.items() if qi - keys[t] == W}
+    assert inside and inside <= differs(W - 1), "a window one too short does not show"
+    assert outside and outside <= differs(W + 1), "a window one too long does not show"
+    mixer = lat_mixer(kit, dtype, D, m, eps, page)
+    mixer.load(lambda nm: w[nm].cuda().to(dtype))
+    tol = dict(f32=2e-4, bf16=5e-2)
+    run = MixerRun(kit, mixer, dtype, page)
+    close(run.feed(x, [n], "whole"), want, dtype, **tol)
+    close(run.feed(x, cuts_of(n - 40, [2, 3, 2, 17, 5, 2, 30, 64]) + [1] * 40, "cut"), want, dtype, **tol)
+    close(run.feed(x, cuts_of(n, [33, 7, 65]), "odd"), want, dtype, **tol)
+    xb = x[:130]
+    wb = torch.from_numpy(P.latent_attention(xb.numpy(), npw(w), "p.", m, eps))
+    plan = [{"a": (0, 50), "b": (0, 3)}, {"a": (50, 51), "b": (3, 90)}, {"a": (51, 200), "b": (90, 91)},
+            {"a": (200, 201), "b": (91, 92)}, {"a": (201, n), "b": (92, 130)}]
+    got = MixerRun(kit, mixer, dtype, page).plan({"a": x, "b": xb}, plan)
+    close(got["a"], want, dtype, **tol)
+    close(got["b"], wb, dtype, **tol)
+
+
+# ------------------------------------------------------------------ the matrix memory
+def mem_weights(D, m, seed, f_bias=3.0):
+    g = torch.Generator().manual_seed(seed)
+    r = lambda *s: torch.randn(*s, generator=g)
+    H, d, v = m["heads"], m["dim"], m["vdim"]
+    w = {"q": r(H * d, D) * 1.5 / D ** 0.5, "k": r(H * d, D) * 1.5 / D ** 0.5, "v": r(H * v, D) / D ** 0.5,
+         "g": r(H * v, D) / D ** 0.5, "o": r(D, H * v) / (H * v) ** 0.5, "norm": 1 + 0.2 * r(H * v),
+         "i": r(H, D) * 2.0 / D ** 0.5, "i.b": 0.5 * r(H), "f": r(H, D) * 2.0 / D ** 0.5, "f.b": f_bias + r(H)}
+    return {k: bf(x) for k, x in w.items()}
+
+
+def mem_mixer(kit, dtype, D, m, eps, page=16, max_tokens=640):
+    return kit.parts.build_mixer(kit.parts.PartSpec("mlstm", {
+        "hidden_size": D, "num_heads": m["heads"], "head_dim": m["dim"], "v_head_dim": m["vdim"], "gate_cap": m["gate_cap"],
+        "eps": eps}), ctx_for(kit, dtype, page, max_tokens))
+
+
+# width, heads, key size, value size, cap
+MEM_SHAPES = [(64, 2, 16, 24, 8.0), (128, 4, 32, 32, 15.0), (100, 3, 20, 11, 5.0), (192, 2, 128, 64, 10.0), (72, 5, 12, 63, 2.0),
+              (96, 1, 200, 31, 12.0)]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", MEM_SHAPES)
+def test_matrix_memory_in_portions_and_token_by_token(kit, dtype, shape):
+    """The whole sequence in one step, in portions down to two tokens, token by token (more than one scan of 32
+    tokens in a portion, too), and two sequences beside each other: S, n and m carry over in the request's slot."""
+    D, H, d, v, cap = shape
+    m, eps = {"heads": H, "dim": d, "vdim": v, "gate_cap": cap}, 1e-5
+    w = mem_weights(D, m, seed=61)
+    mixer = mem_mixer(kit, dtype, D, m, eps)
+    assert set(mixer.weights()) == set(w)
+    mixer.load(lambda n: w[n].cuda().to(dtype))
+    g = torch.Generator().manual_seed(62)
+    xa, xb = bf(torch.randn(75, D, generator=g) * 2), bf(torch.randn(41, D, generator=g) * 2)
+    wa = torch.from_numpy(P.mlstm(xa.numpy(), npw(w), "p.", m, eps))
+    wb = torch.from_numpy(P.mlstm(xb.numpy(), npw(w), "p.", m, eps))
+    uncapped = P.mlstm(xa.numpy(), npw(w), "p.", dict(m, gate_cap=1e4), eps)
+    if cap <= 5:
+        assert np.abs(uncapped - wa.numpy()).max() > 0.02 * wa.abs().max(), "the cap of the gates does not show"
+    # bfloat16: q, k and v are rounded before a division by |n . q|, which can be small: the largest error of 5000 values
+    tol = dict(f32=2e-4, bf16=8e-2)
+    run = MixerRun(kit, mixer, dtype, 16)
+    close(run.feed(xa, [75], "whole"), wa, dtype, **tol)
+    close(run.feed(xa, cuts_of(75, [2, 3, 2, 17, 5, 2, 40]), "cut"), wa, dtype, **tol)
+    close(run.feed(xa, [1] * 75, "single"), wa, dtype, **tol)
+    got = MixerRun(kit, mixer, dtype, 16).plan({"a": xa, "b": xb}, TWO)
+    close(got["a"], wa, dtype, **tol)
+    close(got["b"], wb, dtype, **tol)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_matrix_memory_remembers_far_back_and_slots_start_clean(kit, dtype):
+    """Forget gates near 1 keep what an early token wrote for hundreds of tokens (the plain result changes when the
+    first tokens are cut off); a slot that is freed and used again starts from zeros and m = 0."""
+    D, m, eps = 64, {"heads": 2, "dim": 32, "vdim": 16, "gate_cap": 12.0}, 1e-5
+    w = mem_weights(D, m, seed=63, f_bias=9.0)
+    mixer = mem_mixer(kit, dtype, D, m, eps)
+    mixer.load(lambda n: w[n].cuda().to(dtype))
+    g = torch.Generator().manual_seed(64)
+    x = bf(torch.randn(400, D, generator=g))
+    want = torch.from_numpy(P.mlstm(x.numpy(), npw(w), "p.", m, eps))
+    cut = P.mlstm(x.numpy()[8:], npw(w), "p.", m, eps)
+    assert np.abs(cut[-1] - want.numpy()[-1]).max() > 0.02 * np.abs(want.numpy()[-1]).max(), "the first tokens are forgotten"
+    run = MixerRun(kit, mixer, dtype, 16, slots=1)
+    tol = dict(f32=5e-4, bf16=5e-2)
+    close(run.feed(x, cuts_of(360, [64, 2, 130, 3]) + [1] * 40, "one"), want, dtype, **tol)
+    y = bf(torch.randn(50, D, generator=g))
+    close(run.feed(y, [20, 30], "two"), P.mlstm(y.numpy(), npw(w), "p.", m, eps), dtype, **tol)      # the same slot again
+
+
+# ------------------------------------------------------------------ whole models through bin/trace_run
+LENGTHS = {"fiv_a": [1, 5, 37, 70, 130, 96], "fiv_b": [2, 64, 65, 231, 90, 33], "fiv_c": [3, 66, 40, 150, 97, 29],
+           "fiv_d": [4, 17, 290, 33, 65, 140]}
+# float32: every row to a few units of rounding.  bfloat16: nine rows in ten within 4 % of the row's largest logit
+# and none further off than what a lost key or state would cause (such a row is off by its whole size).
+TOL = {"float32": (1e-4, 1e-4), "bfloat16": (4e-2, 0.15)}
+_CASES = {}
+
+
+def case(name, seed):
+    if (name, seed) not in _CASES:
+        cfg, page = ft.get(name)
+        weights = ft.random_weights(cfg, seed=seed)
+        requests = tt.random_requests(cfg["vocab"], LENGTHS[name], seed=seed + 100)
+        w = ft.as_numpy(weights)
+        reference = {r: P.forward(cfg, w, toks) for r, toks in requests.items()}
+        _CASES[(name, seed)] = (cfg, page, weights, requests, reference)
+    return _CASES[(name, seed)]
+
+
+def compare(trace, out_dir, reference, vocab, dtype):
+    errs = []
+    for step, exp in trace.expect.items():
+        path = os.path.join(out_dir, f"{step}.f32")
+        assert os.path.exists(path), f"step {step} wrote no file"
+        got = np.fromfile(path, dtype="<f4").reshape(-1, vocab)
+        assert got.shape[0] == len(exp), f"step {step}: {got.shape[0]} rows, expected {len(exp)}"
+        for row, (name, pos) in zip(got, exp):
+            ref = reference[name][pos]
+            assert np.isfinite(row).all(), f"step {step} {name}@{pos}: non-finite logits"
+            errs.append((float(np.abs(row - ref).max() / max(np.abs(ref).max(), 1e-6)), step, name, pos))
+    most, worst = TOL[dtype]
+    p90 = float(np.percentile([e[0] for e in errs], 90))
+    top = max(errs)
+    assert p90 <= most, f"90th percentile of the rows' errors is {p90:.3e}"
+    assert top[0] <= worst, f"worst relative error {top[0]:.3e} at (step, request, position) {top[1:]}"
+    return p90, top[0]
+
+
+def test_the_plain_model_feels_every_mechanism():
+    """Leaving out the sink, the blend of values, the gates of the residual or the embedding's scale changes the
+    plain logits: a replay that passes has them all."""
+    cfg, page, weights, requests, reference = case("fiv_a", 81)
+    w, toks = ft.as_numpy(weights), requests["r3"]
+    base = reference["r3"]
+    def off(change):
+        w2 = dict(w)
+        change(w2)
+        return np.abs(P.forward(cfg, w2, toks) - base).max() / np.abs(base).max()
+    assert off(lambda x: x.update({"l1.mix.sink": x["l1.mix.sink"] - 30})) > 1e-2
+    assert off(lambda x: x.update({"l3.mix.vmix": np.array(0.0)})) > 1e-2
+    assert off(lambda x: x.update({"l2.rg1.b": x["l2.rg1.b"] + 30})) > 1e-2
+    assert off(lambda x: x.update({"l0.mlp.down.b": x["l0.mlp.down.b"] * 0})) > 1e-3
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", sorted(ft.TINY))
+def test_replay_matches_plain(tmp_path, cuda_device, name, dtype):
+    """Whole prompts; prompts with their last 48 tokens one by one (every window and chunk passes over decoded
+    tokens); portions down to two tokens; and two mixed schedules with up to four and three live requests on a
+    pool of the trace's peak, where pages and slots are used again."""
+    cfg, page, weights, requests, reference = case(name, 81)
+    model_dir = ft.model_folder(tmp_path, name, cfg, weights)
+    trace = tt.Trace()
+    tt.whole(trace, requests)
+    tt.tail_decode(trace, requests, tail=48)
+    tt.portions(trace, requests)
+    tt.mixed(trace, requests, max_live=4, seed=3)
+    tt.mixed(trace, dict(reversed(list(requests.items()))), max_live=3, seed=4, tag="n")
+    out = str(tmp_path / "out")
+    tt.run_trace(model_dir, dtype, trace, out, block_size=page)
+    p90, worst = compare(trace, out, reference, cfg["vocab"], dtype)
+    pool, asked, shared = tt.pages_were_used_again(trace, out + "/pages.jsonl", page)
+    print(f"{name} {dtype}: {len(trace.steps)} steps, {pool} pages for {asked} asked, {shared} held by several, "
+          f"errors: 90 % within {p90:.2e}, worst {worst:.2e}")
+
+
+@pytest.mark.parametrize("name,dtype", [("fiv_a", "bfloat16"), ("fiv_c", "float32"), ("fiv_b", "bfloat16")])
+def test_pages_given_back_are_never_read(tmp_path, cuda_device, name, dtype):
+    """The mixed trace with every page overwritten by NaN the moment it is given back (the windowed layers give
+    pages back all the time)."""
+    cfg, page, weights, requests, reference = case(name, 81)
+    model_dir = ft.model_folder(tmp_path, name, cfg, weights)
+    trace = tt.Trace()
+    tt.mixed(trace, requests, max_live=4, seed=7)
+    tt.portions(trace, requests)
+    out = str(tmp_path / "out")
+    tt.run_trace(model_dir, dtype, trace, out, block_size=page, env=dict(os.environ, GOLLMGO_B200_POISON_FREED="1"))
+    compare(trace, out, reference, cfg["vocab"], dtype)
+    tt.pages_were_used_again(trace, out + "/pages.jsonl", page)
+
+
+# ------------------------------------------------------------------ the entry point
+def plain_greedy(cfg, weights, prompt, n):
+    w = ft.as_numpy(weights)
+    toks = list(prompt)
+    for _ in range(n):
+        toks.append(int(P.forward(cfg, w, toks)[-1].argmax()))
+    return toks[len(prompt):]
+
+
+def test_greedy_generation_through_the_engine(tmp_path, cuda_device):
+    """Requests of unequal length through Engine.generate (scheduler, chunked prompts, captured decode steps, the
+    device's arg-max): the plain implementation's tokens, alone and together."""
+    from gollmgo_b200 import Engine, SamplingParams
+    cfg, page = ft.get("fiv_a")
+    weights = ft.random_weights(cfg, seed=83)
+    d = ft.model_folder(tmp_path, "fiv_a", cfg, weights)
+    prompts = list(tt.random_requests(cfg["vocab"], [1, 9, 40, 23], seed=8).values())
+    eng = Engine(d, dtype="float32", block_size=page, num_blocks=24, max_batch_size=4, max_token_budget=32,
+                 prefill_chunk_size=16)
+    outs = eng.generate(prompts, SamplingParams(max_tokens=12, ignore_eos=True))
+    want = [plain_greedy(cfg, weights, pr, 12) for pr in prompts]
+    assert [o.token_ids for o in outs] == want
+    assert eng.generate([prompts[2]], SamplingParams(max_tokens=12, ignore_eos=True))[0].token_ids == want[2]
+    eng.runner.cache.audit()
+    assert eng.runner.cache.min_free_pages() == 24
+    assert eng.runner.cache.slots.num_free == eng.runner.cache.slots.max_requests
+
+
+def test_long_decoding_in_bfloat16_stays_near_the_plain_choice(tmp_path, cuda_device):
+    """200 decoded tokens, past every window and chunk and over many pages, through captured decode steps: the
+    tokens are (nearly) the plain implementation's best given the same history."""
+    from gollmgo_b200 import Engine, SamplingParams
+    cfg, page = ft.get("fiv_b")
+    weights = ft.random_weights(cfg, seed=84)
+    d = ft.model_folder(tmp_path, "fiv_b", cfg, weights)
+    prompt = tt.random_requests(cfg["vocab"], [11], seed=9)["r0"]
+    eng = Engine(d, dtype="bfloat16", block_size=page, num_blocks=40, max_batch_size=2, max_token_budget=64)
+    toks = eng.generate([prompt], SamplingParams(max_tokens=200, ignore_eos=True))[0].token_ids
+    assert len(toks) == 200
+    logits = P.forward(cfg, ft.as_numpy(weights), prompt + toks)
+    near = sum(float(row.max() - row[tok]) <= 0.06 * float(np.abs(row).max())
+               for tok, row in zip(toks, logits[len(prompt) - 1:]))
+    assert near >= 185, f"only {near} of 200 tokens are near the plain choice"
+    assert eng.runner.cache.min_free_pages() == 40
+
+
+def test_command_line_generates(tmp_path, cuda_device):
+    import json
+    import subprocess
+    import sys
+    cfg, page = ft.get("fiv_c")
+    weights = ft.random_weights(cfg, seed=85)
+    d = ft.model_folder(tmp_path, "fiv_c", cfg, weights)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    p = subprocess.run([sys.executable, "-m", "gollmgo_b200", "generate", "--model", d, "--dtype", "float32",
+                        "--block-size", str(page), "--num-blocks", "16", "--max-batch-size", "4", "--max-token-budget", "64",
+                        "--log-level", "error", "--prompt-ids", "5,6,7", "--prompt-ids", "9", "--max-tokens", "5", "--ignore-eos"],
+                       capture_output=True, text=True, cwd=root)
+    assert p.returncode == 0, p.stderr
+    lines = [json.loads(l) for l in p.stdout.strip().splitlines()]
+    assert lines[0]["token_ids"] == plain_greedy(cfg, weights, [5, 6, 7], 5)
+    assert lines[1]["token_ids"] == plain_greedy(cfg, weights, [9], 5)
