@@ -159,10 +159,14 @@ def reference_arm(args) -> int:
 # (the layers of its repeated run counted once per pass).  Fapudra: the Bevuvik shape of equal width,
 # heads, kv heads, head size and number of layer runs (it has the attention beside a delta rule and the
 # recurrent state; its dense feed-forward is as wide as the two experts a Fapudra token uses together).
+# Fivesun: the Bevuvik shape of equal width, heads, kv heads, head size, feed-forward width, vocabulary and
+# number of layer runs (it has the attention on the same kernels, a recurrent matrix state of equal size
+# per head and the dense gated feed-forward).
 DESIGN_PAIRS = {
     "tekenex": [("tekenex_w2048", "llama_mqa_w2048"), ("tekenex_w4096", "llama_mqa_w4096")],
     "bevuvik": [("bevuvik_w2048", "llama_gqa_w2048"), ("bevuvik_w4096", "llama_gqa_w4096")],
     "fapudra": [("fapudra_w2048", "bevuvik_w2048"), ("fapudra_w4096", "bevuvik_w4096")],
+    "fivesun": [("fivesun_w2048", "bevuvik_w2048"), ("fivesun_w4096", "bevuvik_w4096")],
 }
 
 

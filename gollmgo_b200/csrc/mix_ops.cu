@@ -393,9 +393,37 @@ __global__ void gated_act_kernel(const TA* __restrict__ gu, const float* __restr
   }
 }
 
+// 16 bytes of gates and of ups a thread (I a multiple of that many values, rows 16-byte aligned)
+template <typename TA>
+__global__ void gated_act_vec_kernel(const TA* __restrict__ gu, const float* __restrict__ bias, TA* __restrict__ out, int I, int kind) {
+  constexpr int VPT = 16 / (int)sizeof(TA);
+  pdl_trigger();
+  pdl_wait();
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * VPT;
+  if (c >= I) return;
+  const size_t t = blockIdx.y;
+  uint4 gr = *reinterpret_cast<const uint4*>(gu + t * 2 * I + c), ur = *reinterpret_cast<const uint4*>(gu + t * 2 * I + I + c), r;
+  const TA* gv = reinterpret_cast<const TA*>(&gr);
+  const TA* uv = reinterpret_cast<const TA*>(&ur);
+  TA* rv = reinterpret_cast<TA*>(&r);
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    const float g = to_f32(gv[j]) + (bias ? bias[c + j] : 0.f), u = to_f32(uv[j]) + (bias ? bias[I + c + j] : 0.f);
+    rv[j] = from_f32<TA>(gated_act_apply(g, kind) * u);
+  }
+  *reinterpret_cast<uint4*>(out + t * I + c) = r;
+}
+
 extern "C" int gg_gated_act(const void* gu, const float* bias, void* out, int T, int I, int kind, int dtype, cudaStream_t stream) {
   GG_REQUIRE(T >= 0 && I > 0 && gu && out && kind >= 0 && kind <= 2, "gated_act: bad arguments T=%d I=%d kind=%d", T, I, kind);
   if (T == 0) return GG_OK;
+  const int vpt = dtype == GG_F32 ? 4 : 8;
+  if ((dtype == GG_F32 || dtype == GG_BF16) && I % vpt == 0 && T <= 65535 && ((size_t)gu % 16) == 0 && ((size_t)out % 16) == 0) {
+    const dim3 grid((I / vpt + 255) / 256, T);
+    if (dtype == GG_F32) gg_launch(gated_act_vec_kernel<float>, grid, dim3(256), 0, stream, (const float*)gu, bias, (float*)out, I, kind);
+    else gg_launch(gated_act_vec_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, (const __nv_bfloat16*)gu, bias, (__nv_bfloat16*)out, I, kind);
+    return gg_check_launch("gated_act");
+  }
   int gx = (I + 255) / 256;
   if (gx > 64) gx = 64;
   for (int t0 = 0; t0 < T; t0 += 65535) {

@@ -10,7 +10,7 @@
 //
 // gg_mlstm_gates: i = cap tanh((zi + bi) / cap), f = logsigmoid(cap tanh((zf + bf) / cap)) (cap <= 0: no
 //   cap), the maxima m_t of every sequence's tokens of the step from the m its state slot holds
-//   (a warp per (sequence, head): the map m -> max(i, f + m) composes, so 32 tokens are one scan),
+//   (a block per (sequence, head): the map m -> max(i, f + m) composes, so a warp's 32 tokens are one scan),
 //   beta, g and m_t per token, and the new m into the slot.
 // gg_mlstm_rows: rows [q | k | v] of the projection (activation type) to float32 rows
 //   [q * qscale | k | v, 1, 0..] with the value heads padded to dvp columns.
@@ -22,24 +22,27 @@
 __device__ __forceinline__ float mlstm_cap(float z, float cap) { return cap > 0.f ? cap * tanhf(z / cap) : z; }
 __device__ __forceinline__ float mlstm_logsigmoid(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
 
-// grid (B, ceil(H / 4)), 128 threads: warp = head
-__global__ void __launch_bounds__(128)
+// grid (B, H), 32 * NW threads: a warp scans 32 tokens, the block's warps 32 * NW tokens at a time; what a warp's
+// tokens do to m together (its last lane's composed map) goes through shared memory, and every warp folds the maps
+// of the warps before it over the maximum carried in
+__global__ void __launch_bounds__(1024)
 mlstm_gates_kernel(const float* __restrict__ zi, long long zi_stride, const float* __restrict__ zf, long long zf_stride,
                    const float* __restrict__ bi, const float* __restrict__ bf, float cap, float* __restrict__ m_state,
                    const int* __restrict__ cu_q_lens, const int* __restrict__ context_lens,
                    const int* __restrict__ state_slots, int H, float* __restrict__ beta, float* __restrict__ decay,
                    float* __restrict__ m_out) {
+  __shared__ float aggA[32], aggB[32];
   pdl_trigger();
-  const int b = blockIdx.x, lane = threadIdx.x & 31, h = blockIdx.y * 4 + (threadIdx.x >> 5);
+  const int b = blockIdx.x, h = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, NW = blockDim.x >> 5;
   const int slot = state_slots[b];
   const int t0 = cu_q_lens[b], qlen = cu_q_lens[b + 1] - t0;
   pdl_wait();
-  if (h >= H || slot < 0 || qlen <= 0) return;
+  if (slot < 0 || qlen <= 0) return;
   const int start = context_lens[b] - qlen;
   float carry = start > 0 ? m_state[(size_t)slot * H + h] : 0.f;        // a new sequence starts from m = 0
   const float bih = bi ? bi[h] : 0.f, bfh = bf ? bf[h] : 0.f;
-  for (int c0 = 0; c0 < qlen; c0 += 32) {
-    const int tt = c0 + lane;
+  for (int p0 = 0; p0 < qlen; p0 += 32 * NW) {
+    const int tt = p0 + warp * 32 + lane;
     const bool live = tt < qlen;
     float gi = 0.f, gf = 0.f;
     if (live) {
@@ -53,18 +56,23 @@ mlstm_gates_kernel(const float* __restrict__ zi, long long zi_stride, const floa
       const float Ae = __shfl_up_sync(0xffffffffu, A, o), Be = __shfl_up_sync(0xffffffffu, Bm, o);
       if (lane >= o) { Bm = fmaxf(Bm, A + Be); A += Ae; }
     }
-    const float m = fmaxf(Bm, A + carry);
+    if (lane == 31) { aggA[warp] = A; aggB[warp] = Bm; }
+    __syncthreads();
+    float m_in = carry;
+    for (int j = 0; j < warp; ++j) m_in = fmaxf(aggB[j], aggA[j] + m_in);
+    const float m = fmaxf(Bm, A + m_in);
     float prev = __shfl_up_sync(0xffffffffu, m, 1);
-    if (lane == 0) prev = carry;
+    if (lane == 0) prev = m_in;
     if (live) {
       const size_t at = (size_t)(t0 + tt) * H + h;
       beta[at] = expf(gi - m);
       decay[at] = expf(gf + prev - m);
       m_out[at] = m;
     }
-    carry = __shfl_sync(0xffffffffu, m, min(31, qlen - c0 - 1));
+    for (int j = 0; j < NW; ++j) carry = fmaxf(aggB[j], aggA[j] + carry);
+    __syncthreads();
   }
-  if (lane == 0) m_state[(size_t)slot * H + h] = carry;
+  if (threadIdx.x == 0) m_state[(size_t)slot * H + h] = carry;
 }
 
 // grid (T): out row = [q * qscale (H*d) | k (H*d) | per head: v (dv), 1, zeros up to dvp]
@@ -108,12 +116,13 @@ mlstm_out_kernel(const float* __restrict__ o_raw, const float* __restrict__ m_ro
 
 extern "C" int gg_mlstm_gates(const float* zi, long long zi_stride, const float* zf, long long zf_stride, const float* bi,
                               const float* bf, float cap, float* m_state, const int* cu_q_lens, const int* context_lens,
-                              const int* state_slots, int B, int H, float* beta, float* decay, float* m_out,
+                              const int* state_slots, int B, int H, int T, float* beta, float* decay, float* m_out,
                               cudaStream_t stream) {
   GG_REQUIRE(B > 0 && H > 0 && zi && zf && m_state && beta && decay && m_out, "mlstm_gates: bad arguments B=%d H=%d", B, H);
   GG_REQUIRE(zi_stride >= H && zf_stride >= H, "mlstm_gates: gate rows shorter than %d heads", H);
-  GG_REQUIRE((H + 3) / 4 <= 65535, "mlstm_gates: too many heads");
-  gg_launch(mlstm_gates_kernel, dim3(B, (H + 3) / 4), dim3(128), 0, stream, zi, zi_stride, zf, zf_stride, bi, bf, cap, m_state,
+  GG_REQUIRE(H <= 65535 && T >= 0, "mlstm_gates: too many heads");
+  const int warps = T > 4 * B ? 16 : 1;          // a step with prompt portions: 512 tokens of a sequence at a time
+  gg_launch(mlstm_gates_kernel, dim3(B, H), dim3(32 * warps), 0, stream, zi, zi_stride, zf, zf_stride, bi, bf, cap, m_state,
             cu_q_lens, context_lens, state_slots, H, beta, decay, m_out);
   return gg_check_launch("mlstm_gates");
 }

@@ -1096,7 +1096,7 @@ def mlstm_gates(zi: torch.Tensor, zf: torch.Tensor, bias_i: Optional[torch.Tenso
         raise KernelError("mlstm_gates: float32 gate rows, m_state float32 [slots, heads]")
     _check(lib().gg_mlstm_gates(_p(zi), ctypes.c_longlong(zi.stride(0)), _p(zf), ctypes.c_longlong(zf.stride(0)), _p(bias_i),
                                 _p(bias_f), ctypes.c_float(cap), _p(m_state), _p(cu_q_lens), _p(context_lens),
-                                _p(state_slots), num_seqs, heads, _p(beta), _p(decay), _p(m_out), _stream()))
+                                _p(state_slots), num_seqs, heads, beta.shape[0], _p(beta), _p(decay), _p(m_out), _stream()))
 
 
 def mlstm_rows(x: torch.Tensor, heads: int, d: int, dv: int, dvp: int, qscale: float, out: torch.Tensor) -> None:

@@ -13,7 +13,7 @@ The recurrence is the engine's plain linear recurrence (csrc/delta_rule.cu, the 
 with one more value column that is always 1, so that n is a column of S; the gates, the maxima and the
 normaliser are csrc/mlstm.cu.  State per request, in its state slot: S with n in float32
 [heads, dvp, d] (dvp = dv + 1 rounded up to 4) and m [heads].  Nothing is paged.  The gates' product is
-float32 (its weights are kept so), and so is everything between the projections and the gated rows.
+summed and left in float32, and so is everything between the projections and the gated rows.
 
 params: hidden_size, num_heads, head_dim, v_head_dim, gate_cap (0: none), eps, floor (default 1e-6), out_buffer,
 names (optional dict: q, k, v, i, f, gate, o, norm; the gates' biases are the i, f names + ".b").
@@ -53,7 +53,6 @@ class MatrixMemory:
         self.rows_width = self.nh * (2 * self.d + self.dvp)
         ws, T = ctx.workspace, ctx.max_tokens
         ws.reserve("mlstm_proj", T * self.proj_width, ctx.act_dtype)
-        ws.reserve("mlstm_x32", T * self.hidden, torch.float32)
         ws.reserve("mlstm_if", T * 2 * self.nh, torch.float32)
         ws.reserve("mlstm_rows", T * self.rows_width, torch.float32)
         ws.reserve("mlstm_beta", T * self.nh, torch.float32)
@@ -83,8 +82,7 @@ class MatrixMemory:
         w[:self.qkv_cols] = torch.cat([p.to(dt) for p in parts], dim=0)
         w[self.gate_col:self.gate_col + self.nh * self.dv] = gate.to(dt)
         self.w_proj = w.contiguous()
-        # what enters the recurrence is float32: the two gates' weights are widened once, here
-        self.w_if = torch.cat([get(n["i"]).float(), get(n["f"]).float()], dim=0).contiguous()
+        self.w_if = torch.cat([get(n["i"]), get(n["f"])], dim=0).contiguous()
         self.b_i = get(n["i"] + ".b").float().contiguous()
         self.b_f = get(n["f"] + ".b").float().contiguous()
         self.norm_w = get(n["norm"]).float().contiguous()
@@ -94,13 +92,8 @@ class MatrixMemory:
         T, ws, H = x.shape[0], self.ctx.workspace, self.nh
         state, m_state = cache
         proj = linear(x, self.w_proj, ws.get("mlstm_proj", T, self.proj_width))
-        zif = ws.get("mlstm_if", T, 2 * H)
-        if x.dtype == torch.float32:
-            torch.mm(x, self.w_if.t(), out=zif)
-        else:
-            x32 = ws.get("mlstm_x32", T, self.hidden)
-            x32.copy_(x)
-            torch.mm(x32, self.w_if.t(), out=zif)
+        # the gates' inputs: a product of the activation type's values summed in float32 and left in float32
+        zif = linear(x, self.w_if, ws.get("mlstm_if", T, 2 * H))
         beta, decay, m_row = ws.get("mlstm_beta", T, H), ws.get("mlstm_decay", T, H), ws.get("mlstm_m", T, H)
         B = batch.num_seqs
         ops.mlstm_gates(zif[:, :H], zif[:, H:], self.b_i, self.b_f, self.cap, m_state, batch.cu_q_lens, batch.context_lens,

@@ -121,7 +121,7 @@ def test_feed_forward_part(kit, dtype):
     want = P.gated_mlp(x, w["gate_proj.weight"], w["up_proj.weight"], w["down_proj.weight"])
     close(got, want, dtype)
     with pytest.raises(ValueError, match="activation"):
-        kit.parts.build_feed_forward(kit.parts.PartSpec("gated_mlp", {"hidden_size": 8, "intermediate_size": 8, "activation": "relu"}), ctx)
+        kit.parts.build_feed_forward(kit.parts.PartSpec("gated_mlp", {"hidden_size": 8, "intermediate_size": 8, "activation": "tanh"}), ctx)
 
 
 def test_weight_stored_in_float32_is_multiplied_in_float32(kit):
