@@ -75,7 +75,8 @@ mlstm_gates_kernel(const float* __restrict__ zi, long long zi_stride, const floa
   if (threadIdx.x == 0) m_state[(size_t)slot * H + h] = carry;
 }
 
-// grid (T): out row = [q * qscale (H*d) | k (H*d) | per head: v (dv), 1, zeros up to dvp]
+// grid (T, ceil(C / 1024)), 256 threads, four values a thread: out row = [q * qscale (H*d) | k (H*d) | per head: v (dv), 1,
+// zeros up to dvp], C its length
 template <typename TA>
 __global__ void mlstm_rows_kernel(const TA* __restrict__ x, long long x_stride, int H, int d, int dv, int dvp,
                                   float qscale, float* __restrict__ out) {
@@ -85,10 +86,16 @@ __global__ void mlstm_rows_kernel(const TA* __restrict__ x, long long x_stride, 
   const int qk = H * d, C = 2 * qk + H * dvp;
   const TA* xr = x + t * x_stride;
   float* o = out + t * C;
-  for (int c = threadIdx.x; c < 2 * qk; c += blockDim.x) o[c] = to_f32(xr[c]) * (c < qk ? qscale : 1.f);
-  for (int e = threadIdx.x; e < H * dvp; e += blockDim.x) {
-    const int h = e / dvp, c = e - h * dvp;
-    o[2 * qk + e] = c < dv ? to_f32(xr[2 * qk + h * dv + c]) : (c == dv ? 1.f : 0.f);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int c = blockIdx.y * 1024 + k * 256 + threadIdx.x;
+    if (c >= C) break;
+    if (c < 2 * qk) {
+      o[c] = to_f32(xr[c]) * (c < qk ? qscale : 1.f);
+    } else {
+      const int e = c - 2 * qk, h = e / dvp, j = e - h * dvp;
+      o[c] = j < dv ? to_f32(xr[2 * qk + h * dv + j]) : (j == dv ? 1.f : 0.f);
+    }
   }
 }
 
@@ -132,8 +139,10 @@ extern "C" int gg_mlstm_rows(const void* x, long long x_stride, int dtype, int T
   GG_REQUIRE(T >= 0 && H > 0 && d > 0 && dv > 0 && dvp > dv, "mlstm_rows: bad sizes T=%d H=%d d=%d dv=%d dvp=%d", T, H, d, dv, dvp);
   GG_REQUIRE(x && out && x_stride >= (long long)H * (2 * d + dv), "mlstm_rows: rows of %lld values are too short", x_stride);
   if (T == 0) return GG_OK;
-  if (dtype == GG_F32) gg_launch(mlstm_rows_kernel<float>, dim3(T), dim3(256), 0, stream, (const float*)x, x_stride, H, d, dv, dvp, qscale, out);
-  else if (dtype == GG_BF16) gg_launch(mlstm_rows_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, stream, (const __nv_bfloat16*)x, x_stride, H, d, dv, dvp, qscale, out);
+  const int C = H * (2 * d + dvp);
+  GG_REQUIRE((C + 1023) / 1024 <= 65535, "mlstm_rows: rows of %d values are too long", C);
+  if (dtype == GG_F32) gg_launch(mlstm_rows_kernel<float>, dim3(T, (C + 1023) / 1024), dim3(256), 0, stream, (const float*)x, x_stride, H, d, dv, dvp, qscale, out);
+  else if (dtype == GG_BF16) gg_launch(mlstm_rows_kernel<__nv_bfloat16>, dim3(T, (C + 1023) / 1024), dim3(256), 0, stream, (const __nv_bfloat16*)x, x_stride, H, d, dv, dvp, qscale, out);
   else return gg_fail(GG_ERR_INVALID, "mlstm_rows: unknown dtype %d", dtype);
   return gg_check_launch("mlstm_rows");
 }
