@@ -21,7 +21,8 @@ one product with the three weights stacked.
 
 params: hidden_size, num_heads, head_dim (of q and k, the unrotated part), v_head_dim, kv_rank, scale, eps (of the
 latent's norm), gate (True = "head" | "element" | False), rot_dim, position (PartSpec of the rotated part; its
-``interleaved`` and ``magnitude`` are honoured), window, names: dict of the tensors' local names.
+``interleaved`` and ``magnitude`` are honoured), window, expand (bool: the rotated form as multi-head attention over
+cached per-head keys and values, which a row beyond 256 values takes by itself), names: dict of the tensors' local names.
 """
 from __future__ import annotations
 
@@ -78,9 +79,15 @@ class LatentAttention:
         self.row = self.rank_p + -(-self.rot // 8) * 8
         if self.rot and ctx.act_dtype == torch.bfloat16 and self.row <= 128 and ATTN_POLICY != "general":
             self.row = 64 if self.row <= 64 else 128
-        if self.rot and (self.expanded or self.row > 256):
-            raise ValueError(f"a latent of {self.rank} values with a rotated part of {self.rot} is beyond what the attention "
-                             f"kernels take (256 values a row)")
+        # The rotated form with a row beyond 256 values (or ``expand``): every head's keys [rotated part | expanded
+        # part] and values are cached, and the layer runs as multi-head attention on the general kernels.
+        self.wide = bool(self.rot) and (bool(spec.get("expand")) or self.expanded or self.row > 256)
+        self.dk = -(-self.qh // 8) * 8
+        if self.wide:
+            self.expanded = False
+            if self.dk > 256 or self.vdim > 256:
+                raise ValueError(f"heads of {self.qh} key values or {self.vdim} values are beyond what the attention kernels take (256)")
+            self.row = self.rank_p
         self.dmax = -(-max(self.dim, self.vdim) // 8) * 8
         if self.expanded and self.dmax > 256:
             raise ValueError(f"a latent of {self.rank} values with heads of {self.dim} / {self.vdim} values is beyond "
@@ -101,17 +108,24 @@ class LatentAttention:
         ws.reserve("mixer_out", T * self.hidden, ctx.act_dtype)
         # the attention as the kernels see it: kv heads, query heads per kv head, head size
         self._nkv, self._group, self._d = (self.nh, 1, self.dmax) if self.expanded else (1, self.nh, self.row)
+        if self.wide:
+            self._nkv, self._group, self._d = self.nh, 1, max(self.dk, self.vdim)
         self._ctas_per_split = self._nkv * -(-self._group // 16)
         self._cluster_cap = None
         if ctx.device.type == "cuda":
             self._cluster_cap = [0] + [ops.attn_decode_cluster_capacity(ctx.act_dtype, self._d, s, self._group)
                                        for s in range(1, ops.ATTN_MAX_CLUSTER + 1)]
         esize = torch.empty((), dtype=ctx.act_dtype).element_size()
-        self._tile_bytes = TILE_KEYS * self._d * esize * (2 if self.expanded else 1)
+        self._tile_bytes = TILE_KEYS * self._d * esize * (2 if self.expanded or self.wide else 1)
         rows = max(n * self._splits(n, TILE_KEYS << b) for n in range(1, ctx.max_seqs + 1)
                    for b in range(MAX_TILES.bit_length()))
         ws.reserve("attn_part_o", rows * self.nh * self._d, torch.float32)
         ws.reserve("attn_part_ml", rows * self.nh * 2, torch.float32)
+        if self.wide:
+            self.wide_width = -(-(self.nh * (2 * self.dk + self.vdim)) // 8) * 8
+            ws.reserve("lat_c", T * self.rank_p, ctx.act_dtype)
+            ws.reserve("lat_qkv", T * self.wide_width, ctx.act_dtype)
+            self._iota = torch.arange(T, dtype=torch.int32, device=ctx.device)
         if self.expanded:
             ws.reserve("lat_c", T * self.rank_p, ctx.act_dtype)
             ws.reserve("lat_qkv", T * 3 * self.nh * self.dmax, ctx.act_dtype)
@@ -120,12 +134,14 @@ class LatentAttention:
         self.w_in = self.w_norm = self.w_uk_t = self.w_uv = self.w_o = None
 
     def cache_need(self):
+        if self.wide:
+            return PagedKVNeed(self.nh, self.dk, self.window, v_heads=self.nh, v_head_dim=self.vdim)
         if self.expanded:
             return PagedKVNeed(self.nh, self.dmax, self.window)
         return PagedKVNeed(1, self.row, self.window, shared_kv=True)
 
     def _fast(self):
-        return self.ctx.act_dtype == torch.bfloat16 and self._d in (64, 128) and ATTN_POLICY != "general"
+        return not self.wide and self.ctx.act_dtype == torch.bfloat16 and self._d in (64, 128) and ATTN_POLICY != "general"
 
     def query_tiles(self):
         need = [TILES_GENERAL]
@@ -159,6 +175,9 @@ class LatentAttention:
         n = self.names
         q, dkv = get(n["q"]), get(n["dkv"])
         w = torch.zeros(self.width1, self.hidden, dtype=q.dtype, device=q.device)
+        if self.wide:          # every query head as [rotated part | unrotated part]: the rotation kernel turns a head's first values
+            q3 = q.view(self.nh, self.qh, self.hidden)
+            q = torch.cat([q3[:, self.dim:], q3[:, :self.dim]], dim=1).reshape(self.nh * self.qh, self.hidden)
         w[:self.nh * self.qh] = q
         w[self.col_c:self.col_c + self.rank + self.rot] = dkv
         if self.gate_cols:
@@ -169,7 +188,7 @@ class LatentAttention:
         # to the latent's space with the same grouped product that brings the result back
         self.w_uk_t = get(n["uk"]).view(self.nh, self.dim, self.rank).transpose(1, 2).contiguous()
         self.w_uv = get(n["uv"]).view(self.nh, self.vdim, self.rank).contiguous()
-        self.w_uk = get(n["uk"]).view(self.nh, self.dim, self.rank).contiguous() if self.expanded else None
+        self.w_uk = get(n["uk"]).view(self.nh, self.dim, self.rank).contiguous() if self.expanded or self.wide else None
         self.w_o = get(n["o"]).contiguous()
 
     def _attend(self, q, q_stride, kc, vc, group, batch, o):
@@ -226,7 +245,52 @@ class LatentAttention:
             ops.gate_mul(a, proj[:, self.col_g:self.col_g + self.gate_cols])
         return linear(a, self.w_o, ws.get("mixer_out", T, self.hidden))
 
+    def _forward_wide(self, x, batch, cache, writes_cache):
+        """The rotated form as multi-head attention: per head the keys [rot(shared key part) | Wuk_h c] and the values
+        Wuv_h c are cached; the queries are [rot(rotated part) | unrotated part]."""
+        T, ws = x.shape[0], self.ctx.workspace
+        kc, vc, group = cache
+        nh, R, Rp, dk, rot, vd = self.nh, self.rank, self.rank_p, self.dk, self.rot, self.vdim
+        proj = linear(x, self.w_in, ws.get("lat_proj", T, self.width1))
+        c = ws.get("lat_c", T, Rp)
+        ops.latent_norm_write(proj, self.col_c, R, self.w_norm, self.eps, self._iota[:T], c)      # row t of c: the latent of token t
+        qkv = ws.get("lat_qkv", T, self.wide_width)
+        if dk != self.qh or self.wide_width != nh * (2 * dk + vd):
+            qkv.zero_()                                       # the padding of every head stays zero
+        qkv[:, :nh * dk].view(T, nh, dk)[:, :, :self.qh].copy_(proj[:, :nh * self.qh].view(T, nh, self.qh))
+        k3 = qkv[:, nh * dk:2 * nh * dk].view(T, nh, dk)
+        k3[:, :, :rot].copy_(proj[:, self.col_c + R:self.col_c + R + rot].unsqueeze(1).expand(T, nh, rot))
+        ops.grouped_gemm(c, self.w_uk, qkv[:, nh * dk + rot:], self.dim, R, nh, a_group_cols=0, o_group_cols=dk,
+                         n_padded=self.dim, rows=T)
+        ops.grouped_gemm(c, self.w_uv, qkv[:, 2 * nh * dk:], vd, R, nh, a_group_cols=0, o_group_cols=vd, n_padded=vd, rows=T)
+        ops.rope_kv_write_x(qkv, batch.positions, batch.slot_mapping[group], self.position.rope_table(),
+                            float(getattr(self.position, "magnitude", 1.0)), None, kc, vc, nh, nh, dk, nh, vd,
+                            self.ctx.page_size, self.position.interleaved, writes_cache)
+        a = ws.get("attn_out", T, nh * vd)
+        window, bt = int(self.window or 0), batch.block_tables[group]
+        if batch.num_portions:
+            t16 = batch.tiles[TILES_GENERAL]
+            ops.attn_prefill_x(qkv, self.wide_width, kc, vc, bt, batch.bt_stride, batch.cu_q_lens, batch.context_lens,
+                               t16.seq, t16.q0, t16.count, a, nh, nh, dk, vd, 1, self.ctx.page_size, window, self.scale, 0.0,
+                               allow_mma=False)
+        if batch.num_decode:
+            n = batch.num_decode
+            facts = getattr(batch, "facts", None)
+            longest = facts.max_context if facts is not None else max(s + l for s, l in zip(batch.q_starts, batch.q_lens))
+            splits = self._splits(n, longest)
+            ops.attn_decode_x(qkv, self.wide_width, kc, vc, bt, batch.bt_stride, batch.cu_q_lens, batch.context_lens,
+                              batch.dec_seqs, n, splits, ws.get("attn_part_o", 1, n * nh * splits * vd),
+                              ws.get("attn_part_ml", 1, n * nh * splits * 2), a, nh, nh, dk, vd, 1, self.ctx.page_size, window,
+                              self.scale, 0.0, allow_mma=False)
+        if self.gated:
+            ops.head_gate(a, proj, self.col_g, nh)
+        elif self.gate_cols:
+            ops.gate_mul(a, proj[:, self.col_g:self.col_g + self.gate_cols])
+        return linear(a, self.w_o, ws.get("mixer_out", T, self.hidden))
+
     def forward(self, x, batch, cache, writes_cache=True):
+        if self.wide:
+            return self._forward_wide(x, batch, cache, writes_cache)
         if self.expanded:
             return self._forward_expanded(x, batch, cache, writes_cache)
         T, ws = x.shape[0], self.ctx.workspace

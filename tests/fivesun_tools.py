@@ -3,8 +3,9 @@ order of their layers and in which optional features they have: attention with c
 than a page and with none, partial and full rotation, scaled and unscaled frequencies, one kv head and as
 many as heads, values of another size than keys, with and without blended values (the first blending layer
 not being the model's first layer); latent attention with windows shorter than a page and with none, ranks
-that need padding, one to five heads; matrix memories whose values are no multiple of four; a layer without
-feed-forward; widths that are no multiple of 8; with and without a scaled embedding."""
+that need padding and one beyond what a cache row holds, one to five heads; matrix memories whose values are
+no multiple of four; a layer without feed-forward; widths that are no multiple of 8; with and without a scaled
+embedding."""
 import copy
 import json
 import os
@@ -70,7 +71,8 @@ FIV_C = {"architecture": "Fivesun", "vocab": 150, "width": 100, "norm": {"eps": 
     _layer(_lat(5, 12, 4, 20, 40, 0.25, window=5, base=5000.0), 52),
     _layer(_mem(3, 20, 11, 5.0), None),
     _layer(_att(2, 2, 20, 12, 0.22, rot=_rot(20, 10000.0, 3.0)), 36),
-    _layer(_lat(1, 24, 12, 16, 30, 0.2, base=10000.0, factor=8.0, blend=(32, 8.0, 1.0)), 44),
+    # a latent too wide to be cached as one row of at most 256 values: per-head keys and values are cached instead
+    _layer(_lat(1, 24, 12, 16, 264, 0.2, base=10000.0, factor=8.0, blend=(32, 8.0, 1.0)), 44),
 ]}
 # the widest kernels: heads of 128, a latent row of 128, a memory of 128 x 64; chunks of exactly four pages
 FIV_D = {"architecture": "Fivesun", "vocab": 384, "width": 192, "norm": {"eps": 1e-6}, "embedding": {"scale": 12.0}, "layers": [

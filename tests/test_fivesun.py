@@ -255,8 +255,9 @@ def lat_weights(D, m, seed):
     return {k: bf(x) for k, x in w.items()}
 
 
-def lat_mixer(kit, dtype, D, m, eps, page=16, max_tokens=640):
+def lat_mixer(kit, dtype, D, m, eps, page=16, max_tokens=640, expand=False):
     return kit.parts.build_mixer(kit.parts.PartSpec("latent_attention", {
+        "expand": expand,
         "hidden_size": D, "num_heads": m["heads"], "head_dim": m["dim"], "v_head_dim": m["vdim"], "kv_rank": m["kv_rank"],
         "scale": m["scale"], "eps": eps, "gate": "element", "rot_dim": m["rot_dim"],
         "position": rope_spec(kit, m["rot"], m["rot_dim"]), "window": (m.get("mask") or {}).get("size")}),
@@ -281,13 +282,20 @@ def lat_entry(shape):
     return D, m, page
 
 
+# a latent too wide to be read as one head (with its rotated part more than 256 values): per-head keys and values are cached
+WIDE_LAT_SHAPES = [(128, 2, 16, 8, 24, 260, 40, 10000.0, (4.0, 64, 16.0, 1.0), 16), (96, 3, 20, 12, 16, 300, None, 10000.0, None, 8)]
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("shape", LAT_SHAPES)
-def test_latent_attention_in_portions_and_token_by_token(kit, dtype, shape):
+@pytest.mark.parametrize("shape,expand", [(s, False) for s in LAT_SHAPES + WIDE_LAT_SHAPES] + [(LAT_SHAPES[0], True), (LAT_SHAPES[2], True), (LAT_SHAPES[4], True)])
+def test_latent_attention_in_portions_and_token_by_token(kit, dtype, shape, expand):
+    """The cached row [latent | rotated key part] on the paged kernels, and (``expand``, or a row beyond 256 values) the same
+    layer with per-head keys and values cached instead."""
     D, m, page = lat_entry(shape)
     eps = 1e-5
     w = lat_weights(D, m, seed=51)
-    mixer = lat_mixer(kit, dtype, D, m, eps, page)
+    mixer = lat_mixer(kit, dtype, D, m, eps, page, expand=expand)
+    assert mixer.wide == (expand or m["kv_rank"] > 240)
     assert set(mixer.weights()) == set(w)
     mixer.load(lambda n: w[n].cuda().to(dtype))
     g = torch.Generator().manual_seed(52)
